@@ -5,7 +5,7 @@ pages it holds in which group); it needs no device and is what the CPU tests exe
 `Cache` adds the device storage:
 
 * a group of key/value layers with equal `KVStateSpec`:
-  `storage[layer, k|v, page, kv_head, PAGE_TOKENS, head_dim]` and a page table
+  `storage[layer, plane (k|v), page, kv_head, PAGE_TOKENS, head_dim]` and a page table
   `[slot, page index] -> page`; a growing group holds position p in entry p, a ring group
   in entry p % ring, so a sliding-window layer never holds more than its window;
 * a group of layers with equal `FixedStateSpec`: `storage[layer, slot, *shape]`.
@@ -108,7 +108,7 @@ class CacheBook:
 class KVView:
     """What an attention-like mixer gets for one layer."""
     spec: KVStateSpec
-    pool: torch.Tensor          # [2, pages, kv_heads, PAGE_TOKENS, head_dim]
+    pool: torch.Tensor          # [planes, pages, kv_heads, PAGE_TOKENS, head_dim]
     pages: int
     ptab: torch.Tensor          # [slots, pages per sequence] int32
     group: int
@@ -175,7 +175,7 @@ class Cache:
         for g, spec in enumerate(kv_groups):
             layers = counts[("kv", g)]
             self.kv_storage.append(torch.empty(
-                (layers, 2, self.book.group_pages[g], spec.kv_heads, PAGE_TOKENS, spec.head_dim),
+                (layers, spec.planes, self.book.group_pages[g], spec.kv_heads, PAGE_TOKENS, spec.head_dim),
                 dtype=dtype, device=self.device))
             n = self.book.max_seqs * self.book.pages_per_seq[g]
             self.ptabs.append(self.ptab_all[off:off + n].view(self.book.max_seqs, self.book.pages_per_seq[g]))
@@ -262,7 +262,7 @@ class Cache:
             for g, spec in enumerate(self.kv_specs):
                 layers = self.kv_storage[g].shape[0]
                 visible = min(length, spec.window) if spec.window > 0 else length
-                total += layers * 2 * visible * spec.kv_heads * spec.head_dim * self.kv_storage[g].element_size()
+                total += layers * spec.planes * visible * spec.kv_heads * spec.head_dim * self.kv_storage[g].element_size()
             for store in self.fixed_storage:
                 total += store[:, slot].numel() * store.element_size()
         return total

@@ -3,8 +3,9 @@
 A mixer returns one of these from `state_spec()` (or None).  The cache puts every layer with
 an equal spec into one group with storage of its own:
 
-* `KVStateSpec(kv_heads, head_dim, window=0)`: keys and values of every position (window 0)
-  or of the last `window` positions only (a ring).  catena-models keeps one full-capacity
+* `KVStateSpec(kv_heads, head_dim, window=0, planes=2)`: keys and values of every position (window 0)
+  or of the last `window` positions only (a ring); `planes=1` keeps one row per position (a latent
+  from which a mixer reads keys and values alike).  catena-models keeps one full-capacity
   region per attention layer and only bounds the traversal of sliding layers
   (src/lfm3.rs:317-328, 901-1046); the ring is this build's own storage choice.
 * `FixedStateSpec(shape, dtype)`: a constant number of bytes per sequence, whatever its
@@ -32,6 +33,7 @@ class KVStateSpec:
     kv_heads: int
     head_dim: int
     window: int = 0            # 0: every position is kept
+    planes: int = 2            # rows kept per position and head: a key and a value, or 1 for a mixer that reads both out of one row
 
     @property
     def ring(self):

@@ -1,0 +1,34 @@
+// What the kernels of the latent attention take (latent.cu, latent_mma.cu); the Python binding fills the same
+// record (kernels._LatentArgs).
+#pragma once
+#include <cuda_runtime.h>
+
+struct LatentArgs {
+    // the step's rows
+    const void* proj;            // [rows][ld_proj]: the low-rank query row (QR), the low-rank key/value row (KR + R), ...
+    long long ld_proj;
+    int q_off, kv_off;           // columns where the two begin
+    void* cq;                    // [rows][QR]: the normed query latent, for the product that makes the heads' queries
+    const float *wq_norm, *wkv_norm;   // [QR], [KR]
+    const float* rate;           // [R / 2]: angle of pair i = position * rate[i] (0: the pair stays)
+    void* q;                     // [rows][H][D + R] the heads' queries as the product left them
+    long long ldq;
+    float* qa;                   // [rows][H][E], E = KR + R: per head the query against the latent, then its turned part
+    long long ldqa;
+    const void* gate;            // [rows][ld_gate], one logit per head (null: no gate)
+    long long ld_gate;
+    float* out;                  // [rows][H][KR]: sum of the weights times the latents, times sigmoid(gate)
+    long long ldo;
+    // geometry
+    int H, D, R, KR, QR, E, EC;  // EC: a cache entry's size (the latent, the turned key part, zeros up to a multiple of 8)
+    float eps, scale;
+    long long rows;
+    // the step and the cache
+    const int *tok_pos, *tok_seq, *seq_start, *seq_pos0, *seq_end, *seq_slot;
+    void* pool;                  // [pages][PAGE_TOKENS][EC]
+    const int* ptab;             // [slots][ptab_stride]
+    long long ptab_stride;
+    int B, max_len;              // sequences; the longest run of new rows (the grid's bound)
+    int splits, chunk;           // keys [s * chunk, (s + 1) * chunk) belong to split s; splits == 1: one block walks them all
+    float* parts;                // splits > 1: [rows * H][splits][2 + KR] (maximum, sum, unnormalised output)
+};

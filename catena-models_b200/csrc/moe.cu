@@ -22,15 +22,79 @@
 #define MOE_TN 64
 #define MOE_BK 16
 #define MOE_THREADS 256
+#define MOE_MAX_GROUPS 64          // groups of experts a router can have
 
 // ------------------------------------------------------------------------------ routing
+// How a token's experts are chosen from its E router logits, and what their weights are.
+struct RouteRule {
+    int softmax_gate;          // scores: softmax over the experts (1) or a sigmoid of each logit (0)
+    int renormalize;           // weights divided by (their sum + renorm_eps)
+    float renorm_eps;
+    float scale;               // factor on the weights
+    const float* correction;   // null, or [E]: added to the scores for the choice only; the weights are the scores themselves
+    int groups, keep;          // groups > 0: the experts form `groups` equal groups of neighbours, a group's score is its largest
+                               // choice score, and only experts of the best `keep` groups can be chosen
+    int real;                  // experts real .. E-1 are identity experts: they get a weight but no rows (their output is the input)
+};
+
+// One thread's walk for one token.  sc [E]: logits in, scores out (overwritten).  ch: [E] scratch for the choice scores when
+// the rule has a correction or groups, else the same array as sc.  Writes ids and wts [top]; counts every chosen real expert.
+__device__ void choose_experts(float* sc, float* ch, int E, int top, const RouteRule& r, int* ids, float* wts, int* counts) {
+    if (r.softmax_gate) {
+        float mx = -INFINITY, den = 0.f;
+        for (int e = 0; e < E; ++e) mx = fmaxf(mx, sc[e]);
+        for (int e = 0; e < E; ++e) den += expf(sc[e] - mx);
+        for (int e = 0; e < E; ++e) sc[e] = expf(sc[e] - mx) / den;
+    } else {
+        for (int e = 0; e < E; ++e) sc[e] = sigmoid_f32(sc[e]);
+    }
+    if (ch != sc)
+        for (int e = 0; e < E; ++e) ch[e] = sc[e] + (r.correction ? r.correction[e] : 0.f);
+    if (r.groups > 0) {
+        // the `keep` best groups stay open: a group is closed if `keep` others have a larger best choice score (or an
+        // equal one and a lower index); a closed group's choice scores count as minus infinity
+        const int n = E / r.groups;
+        float best[MOE_MAX_GROUPS];
+        for (int g = 0; g < r.groups; ++g) {
+            best[g] = -INFINITY;
+            for (int e = g * n; e < (g + 1) * n; ++e) best[g] = fmaxf(best[g], ch[e]);
+        }
+        for (int g = 0; g < r.groups; ++g) {
+            int ahead = 0;
+            for (int o = 0; o < r.groups; ++o)
+                if (o != g && (best[o] > best[g] || (best[o] == best[g] && o < g))) ++ahead;
+            if (ahead >= r.keep)
+                for (int e = g * n; e < (g + 1) * n; ++e) ch[e] = -INFINITY;
+        }
+    }
+    float total = 0.f;
+    for (int j = 0; j < top; ++j) {
+        int best = 0;
+        float bv = -INFINITY;
+        for (int e = 0; e < E; ++e)
+            if (ch[e] > bv) {
+                bv = ch[e];
+                best = e;
+            }
+        ids[j] = best;
+        wts[j] = sc[best];
+        total += sc[best];
+        ch[best] = -INFINITY;
+        if (best < r.real) atomicAdd(counts + best, 1);
+    }
+    if (r.renormalize)
+        for (int j = 0; j < top; ++j) wts[j] /= total + r.renorm_eps;
+    if (r.scale != 1.f)
+        for (int j = 0; j < top; ++j) wts[j] *= r.scale;
+}
+
 // One block per token.  ids[p] = expert of pair p (-1 for rows of padding), wts[p] its weight.
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_router_kernel(int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ counts,
                   const T* __restrict__ h, const T* __restrict__ wr, const int* __restrict__ tok_seq, int W, int E,
-                  int top, int softmax_gate, int renormalize) {
-    extern __shared__ float score[];              // [E]
+                  int top, RouteRule rule) {
+    extern __shared__ float score[];              // [E], and [E] choice scores when the rule needs them
     pdl_trigger();
     pdl_wait();
     const long long t = blockIdx.x;
@@ -49,31 +113,8 @@ moe_router_kernel(int* __restrict__ ids, float* __restrict__ wts, int* __restric
     }
     __syncthreads();
     if (threadIdx.x != 0) return;
-    if (softmax_gate) {
-        float mx = -INFINITY, den = 0.f;
-        for (int e = 0; e < E; ++e) mx = fmaxf(mx, score[e]);
-        for (int e = 0; e < E; ++e) den += expf(score[e] - mx);
-        for (int e = 0; e < E; ++e) score[e] = expf(score[e] - mx) / den;
-    } else {
-        for (int e = 0; e < E; ++e) score[e] = sigmoid_f32(score[e]);
-    }
-    float total = 0.f;
-    for (int j = 0; j < top; ++j) {
-        int best = 0;
-        float bv = -INFINITY;
-        for (int e = 0; e < E; ++e)
-            if (score[e] > bv) {
-                bv = score[e];
-                best = e;
-            }
-        ids[t * top + j] = best;
-        wts[t * top + j] = bv;
-        total += bv;
-        score[best] = -INFINITY;
-        atomicAdd(counts + best, 1);
-    }
-    if (renormalize)
-        for (int j = 0; j < top; ++j) wts[t * top + j] /= total;
+    const bool two = rule.correction || rule.groups > 0;
+    choose_experts(score, two ? score + E : score, E, top, rule, ids + t * top, wts + t * top, counts);
 }
 
 // One block, one thread's walk over the experts: where each expert's rows begin (a multiple of tile_rows: an
@@ -103,14 +144,14 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts, int* __restrict_
 
 // perm[sorted row] = pair, dest[pair] = sorted row (-1 for pairs of padding rows).
 __global__ void moe_scatter_kernel(int* __restrict__ perm, int* __restrict__ dest, int* __restrict__ cursor,
-                                   const int* __restrict__ ids, long long P) {
+                                   const int* __restrict__ ids, long long P, int real) {
     pdl_trigger();
     pdl_wait();
     const long long p = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     if (p >= P) return;
     const int e = ids[p];
     int pos = -1;
-    if (e >= 0) {
+    if (e >= 0 && e < real) {
         pos = atomicAdd(cursor + e, 1);
         perm[pos] = (int)p;
     }
@@ -154,10 +195,12 @@ __global__ void __launch_bounds__(256)
 moe_route_small_kernel(int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ perm, int* __restrict__ dest,
                        int* __restrict__ counts_out, int* __restrict__ plan, int* __restrict__ tile_group,
                        const T* __restrict__ h, const T* __restrict__ wr, const int* __restrict__ tok_seq, int rows, int W,
-                       int E, int top, int softmax_gate, int renormalize, int tile_rows, int max_tiles,
+                       int E, int top, RouteRule rule, int tile_rows, int max_tiles,
                        T* __restrict__ xs, int apply_weight) {
-    extern __shared__ float score[];              // [rows][E], then E counts and E cursors
-    int* counts = reinterpret_cast<int*>(score + rows * E);
+    extern __shared__ float score[];              // [rows][E] (twice when the rule needs choice scores), then E counts and E cursors
+    const bool two = rule.correction || rule.groups > 0;
+    int* counts = reinterpret_cast<int*>(score + (two ? 2 : 1) * rows * E);
+    const int real = rule.real;
     int* cursor = counts + E;
     pdl_trigger();
     pdl_wait();
@@ -179,36 +222,12 @@ moe_route_small_kernel(int* __restrict__ ids, float* __restrict__ wts, int* __re
             continue;
         }
         float* sc = score + t * E;
-        if (softmax_gate) {
-            float mx = -INFINITY, den = 0.f;
-            for (int e = 0; e < E; ++e) mx = fmaxf(mx, sc[e]);
-            for (int e = 0; e < E; ++e) den += expf(sc[e] - mx);
-            for (int e = 0; e < E; ++e) sc[e] = expf(sc[e] - mx) / den;
-        } else {
-            for (int e = 0; e < E; ++e) sc[e] = sigmoid_f32(sc[e]);
-        }
-        float total = 0.f;
-        for (int j = 0; j < top; ++j) {
-            int best = 0;
-            float bv = -INFINITY;
-            for (int e = 0; e < E; ++e)
-                if (sc[e] > bv) {
-                    bv = sc[e];
-                    best = e;
-                }
-            ids[t * top + j] = best;
-            wts[t * top + j] = bv;
-            total += bv;
-            sc[best] = -INFINITY;
-            atomicAdd(counts + best, 1);
-        }
-        if (renormalize)
-            for (int j = 0; j < top; ++j) wts[t * top + j] /= total;
+        choose_experts(sc, two ? sc + rows * E : sc, E, top, rule, ids + t * top, wts + t * top, counts);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
         int n = 0;
-        for (int e = 0; e < E; ++e) {
+        for (int e = 0; e < real; ++e) {              // identity experts get no rows
             const int c = counts[e];
             counts_out[e] = c;
             cursor[e] = n * tile_rows;
@@ -228,7 +247,7 @@ moe_route_small_kernel(int* __restrict__ ids, float* __restrict__ wts, int* __re
     for (int p = threadIdx.x; p < P; p += blockDim.x) {
         const int e = ids[p];
         int pos = -1;
-        if (e >= 0) {
+        if (e >= 0 && e < real) {
             pos = atomicAdd(cursor + e, 1);
             perm[pos] = p;
         }
@@ -252,53 +271,97 @@ static int max_tiles_for(long long pairs, int E, int tile_rows) {
     return (int)(full + (pairs < E ? pairs : E));
 }
 
-// work: int32 scratch of E (counts) + E (cursor) + 1 + 3 * max_tiles (plan) + max_tiles (tile_group) entries;
+// work: int32 scratch of E' (counts) + E' (cursor) + 1 + 3 * max_tiles (plan) + max_tiles (tile_group) entries, E' = E - identity;
 // perm: max_tiles * tile_rows entries (sorted rows), dest: P entries.  tile_rows: 32 for the CUDA-core grouped
 // products of this file, 128 for the tensor-core grouped product.
 // xs (or null): the experts' inputs [max_tiles * tile_rows][W] in the order of the experts, h times the pair's weight
 // when apply_weight (cm_moe_gather as part of this call).
+// E counts every router output; the last `identity` of them are identity experts (no matrices, no rows: their pairs get
+// dest -1 and a weight, see cm_moe_identity).  correction (or null), groups, keep, scale, renorm_eps: see RouteRule.
 extern "C" int cm_moe_route(int dt, int* ids, float* wts, int* perm, int* dest, int* work, const void* h, const void* wr,
                             const int* tok_seq, long long rows, int W, int E, int top, int softmax_gate,
-                            int renormalize, int tile_rows, void* xs, int apply_weight, cudaStream_t st) {
+                            int renormalize, int tile_rows, void* xs, int apply_weight, const float* correction, int groups,
+                            int keep, int identity, float scale, float renorm_eps, cudaStream_t st) {
     if (rows <= 0) return CM_OK;
     if (top < 1 || top > E) CM_REFUSE("moe_route: %d of %d experts", top, E);
-    if ((size_t)E * sizeof(float) > 48 * 1024) CM_REFUSE("moe_route: %d experts", E);
+    if (identity < 0 || identity >= E) CM_REFUSE("moe_route: %d identity experts of %d", identity, E);
+    if (groups < 0 || groups > MOE_MAX_GROUPS || (groups > 0 && (E % groups || keep < 1 || keep > groups || keep * (E / groups) < top)))
+        CM_REFUSE("moe_route: %d groups of which %d stay open, for %d of %d experts", groups, keep, top, E);
+    const bool two = correction || groups > 0;
+    if ((size_t)E * sizeof(float) * (two ? 2 : 1) > 48 * 1024) CM_REFUSE("moe_route: %d experts", E);
     if (tile_rows != MOE_TM && tile_rows != 128) CM_REFUSE("moe_route: row tiles of %d (32 or 128)", tile_rows);
-    const int max_tiles = max_tiles_for(rows * top, E, tile_rows);
-    int *counts = work, *cursor = work + E, *plan = work + 2 * E, *tile_group = plan + 1 + 3 * max_tiles;
-    if (rows <= MOE_SMALL_ROWS && rows * E <= MOE_SMALL_SCORES && (dt == DT_F32 || dt == DT_BF16)) {
-        const size_t small = ((size_t)rows * E) * sizeof(float) + 2 * (size_t)E * sizeof(int);
+    RouteRule rule;
+    rule.softmax_gate = softmax_gate;
+    rule.renormalize = renormalize;
+    rule.renorm_eps = renorm_eps;
+    rule.scale = scale;
+    rule.correction = correction;
+    rule.groups = groups;
+    rule.keep = keep;
+    rule.real = E - identity;
+    // the scratch is laid out for the experts that get rows (the Python side sizes it by their number)
+    const int ER = rule.real;
+    const int max_tiles = max_tiles_for(rows * top, ER, tile_rows);
+    int *counts = work, *cursor = work + ER, *plan = work + 2 * ER, *tile_group = plan + 1 + 3 * max_tiles;
+    if (rows <= MOE_SMALL_ROWS && rows * E * (two ? 2 : 1) <= MOE_SMALL_SCORES && (dt == DT_F32 || dt == DT_BF16)) {
+        const size_t small = ((size_t)rows * E * (two ? 2 : 1)) * sizeof(float) + 2 * (size_t)E * sizeof(int);
         if (dt == DT_F32)
             cm_launch(moe_route_small_kernel<float>, 1, 256, small, st, ids, wts, perm, dest, counts, plan, tile_group,
-                      (const float*)h, (const float*)wr, tok_seq, (int)rows, W, E, top, softmax_gate, renormalize, tile_rows,
+                      (const float*)h, (const float*)wr, tok_seq, (int)rows, W, E, top, rule, tile_rows,
                       max_tiles, (float*)xs, apply_weight);
         else
             cm_launch(moe_route_small_kernel<bf16>, 1, 256, small, st, ids, wts, perm, dest, counts, plan, tile_group,
-                      (const bf16*)h, (const bf16*)wr, tok_seq, (int)rows, W, E, top, softmax_gate, renormalize, tile_rows,
+                      (const bf16*)h, (const bf16*)wr, tok_seq, (int)rows, W, E, top, rule, tile_rows,
                       max_tiles, (bf16*)xs, apply_weight);
         CM_CHECK_LAUNCH();
         return CM_OK;
     }
-    if (cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), st) != cudaSuccess) {
+    if (cudaMemsetAsync(counts, 0, (size_t)ER * sizeof(int), st) != cudaSuccess) {
         cm_set_error("moe_route: memset failed");
         return CM_ERR_LAUNCH;
     }
-    const size_t smem = (size_t)E * sizeof(float);
+    const size_t smem = (size_t)E * sizeof(float) * (two ? 2 : 1);
     if (dt == DT_F32)
         cm_launch(moe_router_kernel<float>, (unsigned)rows, 128, smem, st, ids, wts, counts, (const float*)h, (const float*)wr,
-                  tok_seq, W, E, top, softmax_gate, renormalize);
+                  tok_seq, W, E, top, rule);
     else if (dt == DT_BF16)
         cm_launch(moe_router_kernel<bf16>, (unsigned)rows, 128, smem, st, ids, wts, counts, (const bf16*)h, (const bf16*)wr,
-                  tok_seq, W, E, top, softmax_gate, renormalize);
+                  tok_seq, W, E, top, rule);
     else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();
-    cm_launch(moe_plan_kernel, 1, 32, 0, st, counts, cursor, plan, tile_group, E, tile_rows, max_tiles);
+    cm_launch(moe_plan_kernel, 1, 32, 0, st, counts, cursor, plan, tile_group, ER, tile_rows, max_tiles);
     CM_CHECK_LAUNCH();
     const long long P = rows * top;
-    cm_launch(moe_scatter_kernel, (unsigned)((P + 255) / 256), 256, 0, st, perm, dest, cursor, ids, P);
+    cm_launch(moe_scatter_kernel, (unsigned)((P + 255) / 256), 256, 0, st, perm, dest, cursor, ids, P, rule.real);
     CM_CHECK_LAUNCH();
     if (xs) return cm_moe_gather(dt, xs, h, dest, wts, P, top, W, apply_weight, st);
+    return CM_OK;
+}
+
+// y[t] = (the sum of the weights of token t's pairs whose expert is an identity expert, id >= real) * h[t], float.
+template <typename T>
+__global__ void moe_identity_kernel(float* __restrict__ y, const T* __restrict__ h, const int* __restrict__ ids,
+                                    const float* __restrict__ wts, int top, int real, int K) {
+    pdl_trigger();
+    pdl_wait();
+    const long long t = blockIdx.x;
+    float w = 0.f;
+    for (int j = 0; j < top; ++j)
+        if (ids[t * top + j] >= real) w += wts[t * top + j];
+    for (int c = threadIdx.x; c < K; c += blockDim.x) y[t * K + c] = w * to_f32(h[t * K + c]);
+}
+
+extern "C" int cm_moe_identity(int dt, float* y, const void* h, const int* ids, const float* wts, long long rows, int top,
+                               int real, int K, cudaStream_t st) {
+    if (rows <= 0) return CM_OK;
+    if (dt == DT_F32)
+        cm_launch(moe_identity_kernel<float>, (unsigned)rows, 128, 0, st, y, (const float*)h, ids, wts, top, real, K);
+    else if (dt == DT_BF16)
+        cm_launch(moe_identity_kernel<bf16>, (unsigned)rows, 128, 0, st, y, (const bf16*)h, ids, wts, top, real, K);
+    else
+        return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
     return CM_OK;
 }
 

@@ -98,13 +98,20 @@ __device__ __forceinline__ void warp_row_dots(const T* __restrict__ wrow, const 
     for (int r = 0; r < RP_ROWS; ++r) acc[r] = warp_sum(acc[r]);
 }
 
-// Decay of the decay mix: w = exp(-exp(W2 tanh(W1 x) + w0)), per token and channel, in float.
+// A decay per token and channel out of a low-rank network, in float.  kind 0 (decay mix): w = exp(-exp(W2 tanh(W1 x) + w0));
+// kind 1 (gated linear attention): w = sigmoid(W2 (W1 x) + w0)^(1/tau), formed as exp(log sigmoid(z) / tau).
 // x [rows][W], W1 [R][W], W2 stored transposed [R][C] (neighbouring threads read neighbouring channels), w0 [C];
 // out [rows][C] float.
+__device__ __forceinline__ float log_sigmoid_f32(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+__device__ __forceinline__ float decay_of(float z, int kind, float inv_tau) {
+    return kind == 1 ? expf(log_sigmoid_f32(z) * inv_tau) : expf(-expf(z));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(RP_THREADS)
 lowrank_decay_kernel(float* __restrict__ out, const T* __restrict__ x, const T* __restrict__ w1,
-                     const T* __restrict__ w2, const float* __restrict__ w0, long long rows, int W, int R, int C) {
+                     const T* __restrict__ w2, const float* __restrict__ w0, long long rows, int W, int R, int C, int kind,
+                     float inv_tau) {
     extern __shared__ float th[];                     // [RP_ROWS][R]
     pdl_trigger();
     pdl_wait();
@@ -115,29 +122,31 @@ lowrank_decay_kernel(float* __restrict__ out, const T* __restrict__ x, const T* 
         float acc[RP_ROWS];
         warp_row_dots<T>(w1 + (long long)r * W, x + row0 * W, W, n_rows, W, acc);
         if (lane == 0)
-            for (int i = 0; i < RP_ROWS; ++i) th[i * R + r] = tanhf(acc[i]);
+            for (int i = 0; i < RP_ROWS; ++i) th[i * R + r] = kind == 1 ? acc[i] : tanhf(acc[i]);
     }
     __syncthreads();
     for (int e = threadIdx.x; e < n_rows * C; e += RP_THREADS) {
         const int i = e / C, c = e - i * C;
         float z = 0.f;
         for (int r = 0; r < R; ++r) z = fmaf(to_f32(w2[(long long)r * C + c]), th[i * R + r], z);
-        out[(row0 + i) * C + c] = expf(-expf(z + w0[c]));
+        out[(row0 + i) * C + c] = decay_of(z + w0[c], kind, inv_tau);
     }
 }
 
 extern "C" int cm_lowrank_decay(int dt, float* out, const void* x, const void* w1, const void* w2, const float* w0,
-                                long long rows, int W, int R, int C, cudaStream_t st) {
+                                long long rows, int W, int R, int C, int kind, float tau, cudaStream_t st) {
     if (rows <= 0) return CM_OK;
+    if (kind == 1 && !(tau > 0.f)) CM_REFUSE("lowrank_decay: tau %f", tau);
+    const float inv_tau = kind == 1 ? 1.f / tau : 0.f;
     const size_t smem = (size_t)RP_ROWS * R * sizeof(float);
     if (smem > 48 * 1024) CM_REFUSE("lowrank_decay: rank %d is too large", R);
     const unsigned grid = (unsigned)((rows + RP_ROWS - 1) / RP_ROWS);
     if (dt == DT_F32)
         cm_launch(lowrank_decay_kernel<float>, grid, RP_THREADS, smem, st, out, (const float*)x, (const float*)w1,
-                  (const float*)w2, w0, rows, W, R, C);
+                  (const float*)w2, w0, rows, W, R, C, kind, inv_tau);
     else if (dt == DT_BF16)
         cm_launch(lowrank_decay_kernel<bf16>, grid, RP_THREADS, smem, st, out, (const bf16*)x, (const bf16*)w1,
-                  (const bf16*)w2, w0, rows, W, R, C);
+                  (const bf16*)w2, w0, rows, W, R, C, kind, inv_tau);
     else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();
@@ -155,11 +164,11 @@ __global__ void tanh_inplace_kernel(T* __restrict__ x, long long n) {
 }
 
 __global__ void decay_from_logits_kernel(float* __restrict__ out, const float* __restrict__ z, const float* __restrict__ w0,
-                                         long long n, int C) {
+                                         long long n, int C, int kind, float inv_tau) {
     pdl_trigger();
     pdl_wait();
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-        out[i] = expf(-expf(z[i] + w0[i % C]));
+        out[i] = decay_of(z[i] + w0[i % C], kind, inv_tau);
 }
 
 extern "C" int cm_tanh_inplace(int dt, void* x, long long n, cudaStream_t st) {
@@ -172,16 +181,16 @@ extern "C" int cm_tanh_inplace(int dt, void* x, long long n, cudaStream_t st) {
     return CM_OK;
 }
 
-extern "C" int cm_decay_from_logits(float* out, const float* z, const float* w0, long long rows, int C, cudaStream_t st) {
+extern "C" int cm_decay_from_logits(float* out, const float* z, const float* w0, long long rows, int C, int kind, float tau,
+                                    cudaStream_t st) {
     const long long n = rows * C;
     if (n <= 0) return CM_OK;
+    if (kind == 1 && !(tau > 0.f)) CM_REFUSE("decay_from_logits: tau %f", tau);
     const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-    cm_launch(decay_from_logits_kernel, grid, 256, 0, st, out, z, w0, n, C);
+    cm_launch(decay_from_logits_kernel, grid, 256, 0, st, out, z, w0, n, C, kind, kind == 1 ? 1.f / tau : 0.f);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
-
-__device__ __forceinline__ float log_sigmoid_f32(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
 // Capped gate pre-activations of the matrix memory: z = W h + b for 2 * H rows of W (input gates, then
 // forget gates); out[t][o] = cap * tanh(z / cap), and the logarithm of its sigmoid for the forget gates.
@@ -241,7 +250,9 @@ __device__ __forceinline__ void load_run(const float* p, float* out) {
     }
 }
 
-// MODE 0: decay mix.  MODE 1: matrix memory.  MODE 2: constant decay per head (a.decay [H]).  A block owns some columns of one head's S for one sequence and
+// MODE 0: decay mix.  MODE 1: matrix memory.  MODE 2: constant decay per head (a.decay [H]).  MODE 3: a decay per token and key
+// channel as MODE 0 has it, applied before the output is read: S <- diag(w_t) S + k_t v_t^T, o_t = S^T q_t (gated linear
+// attention).  A block owns some columns of one head's S for one sequence and
 // walks the sequence's rows of the step in order.  Thread (column c, part ks) keeps S[i][c] for the RPT key
 // channels i = ks * RPT ... in registers.  For the matrix memory the block's last column is the normaliser n: it
 // is the column of S whose value channel is constantly one (n <- a n + b k, and its output is n . q), so it needs
@@ -276,7 +287,8 @@ matrix_scan_kernel(const ScanArgs a, int TB) {
     float* sq = sm;                                   // [TB][Dp]
     float* sk = sq + (size_t)TB * Dp;                 // [TB][Dp]
     float* sw = sk + (size_t)TB * Dp;                 // [TB][Dp]  (MODE 0)
-    float* sv = sw + (MODE == 0 ? (size_t)TB * Dp : 0);   // [TB][cols]
+    constexpr bool CH = MODE == 0 || MODE == 3;       // a decay per token and key channel
+    float* sv = sw + (CH ? (size_t)TB * Dp : 0);      // [TB][cols]
     float* sg = sv + (size_t)TB * cols;               // [TB][4]: MODE 1: a = e^(f + m - m'), b = e^(i - m'), e^(-m')
     float* part = sg + (size_t)TB * 4;                // [TB][KS][cols] partial outputs
     const long long per_head = (long long)D * DV + (MODE == 1 ? D + 1 : 0);
@@ -292,22 +304,22 @@ matrix_scan_kernel(const ScanArgs a, int TB) {
     const T* Q = (const T*)a.q + (long long)hd * D;
     const T* K = (const T*)a.k + (long long)hd * D;
     const T* V = (const T*)a.v + (long long)hd * DV + (long long)cb * real;
-    const float* Wd = a.decay + (MODE == 0 ? (long long)hd * D : 0);
+    const float* Wd = a.decay + (CH ? (long long)hd * D : 0);
     const float w_head = MODE == 2 ? a.decay[hd] : 1.f;
     const bool act = MODE == 2 && a.qkv_act;
-    const long long ldw = MODE == 0 ? (long long)H * D : 2LL * H;
+    const long long ldw = CH ? (long long)H * D : 2LL * H;
     float* R = a.raw + (long long)hd * DV + (long long)cb * real;
     const long long ldr = (long long)H * DV;
     const int n_cols = max(0, min(real, DV - cb * real));
     // 16-byte accesses to q, k and the decay: heads of a multiple of 8 channels in rows and buffers aligned to match
-    const bool vec8 = D % 8 == 0 && a.ldq % 8 == 0 && a.ldk % 8 == 0 && (ldw % 8 == 0 || MODE != 0) &&
-                      (((uintptr_t)a.q | (uintptr_t)a.k) & 15) == 0 && (MODE != 0 || ((uintptr_t)a.decay & 31) == 0);
+    const bool vec8 = D % 8 == 0 && a.ldq % 8 == 0 && a.ldk % 8 == 0 && (ldw % 8 == 0 || !CH) &&
+                      (((uintptr_t)a.q | (uintptr_t)a.k) & 15) == 0 && (!CH || ((uintptr_t)a.decay & 31) == 0);
     // channels past D of a staged row are read by the last part's vector accesses: they hold zeros
     for (int e = threadIdx.x; e < TB * (Dp - D); e += SCAN_THREADS) {
         const int tt = e / (Dp - D), i = D + e - tt * (Dp - D);
         sq[(size_t)tt * Dp + i] = 0.f;
         sk[(size_t)tt * Dp + i] = 0.f;
-        if (MODE == 0) sw[(size_t)tt * Dp + i] = 0.f;
+        if (CH) sw[(size_t)tt * Dp + i] = 0.f;
     }
     for (long long t0 = s0; t0 < s1; t0 += TB) {
         const int nt = (int)min((long long)TB, s1 - t0);
@@ -324,7 +336,7 @@ matrix_scan_kernel(const ScanArgs a, int TB) {
                         const int tt = e / D8, i = (e - tt * D8) * 8;
                         load8f<T>(Q + (t0 + tt) * a.ldq + i, fq[u]);
                         load8f<T>(K + (t0 + tt) * a.ldk + i, fk[u]);
-                        if (MODE == 0) load8f<float>(Wd + (t0 + tt) * ldw + i, fw[u]);
+                        if (CH) load8f<float>(Wd + (t0 + tt) * ldw + i, fw[u]);
                     }
                 }
 #pragma unroll
@@ -343,7 +355,7 @@ matrix_scan_kernel(const ScanArgs a, int TB) {
                         for (int x = 0; x < 8; ++x) fq[u][x] *= a.q_scale;
                         store8f<float>(sq + (size_t)tt * Dp + i, fq[u]);
                         store8f<float>(sk + (size_t)tt * Dp + i, fk[u]);
-                        if (MODE == 0) store8f<float>(sw + (size_t)tt * Dp + i, fw[u]);
+                        if (CH) store8f<float>(sw + (size_t)tt * Dp + i, fw[u]);
                     }
                 }
             }
@@ -357,7 +369,7 @@ matrix_scan_kernel(const ScanArgs a, int TB) {
                 }
                 sq[(size_t)tt * Dp + i] = fq * a.q_scale;
                 sk[(size_t)tt * Dp + i] = fk;
-                if (MODE == 0) sw[(size_t)tt * Dp + i] = Wd[(t0 + tt) * ldw + i];
+                if (CH) sw[(size_t)tt * Dp + i] = Wd[(t0 + tt) * ldw + i];
             }
         }
         for (int e = threadIdx.x; e < nt * cols; e += SCAN_THREADS) {
@@ -396,7 +408,7 @@ matrix_scan_kernel(const ScanArgs a, int TB) {
             float q[RPT], k[RPT], w[RPT];
             load_run<RPT>(sq + (size_t)tt * Dp + i0, q);
             load_run<RPT>(sk + (size_t)tt * Dp + i0, k);
-            if (MODE == 0) load_run<RPT>(sw + (size_t)tt * Dp + i0, w);
+            if (CH) load_run<RPT>(sw + (size_t)tt * Dp + i0, w);
             const float vj = sv[tt * cols + c];
             const float af = MODE == 1 ? sg[4 * tt] : w_head, bv = MODE == 1 ? sg[4 * tt + 1] * vj : vj;
             float acc = 0.f;
@@ -407,7 +419,7 @@ matrix_scan_kernel(const ScanArgs a, int TB) {
                     acc = fmaf(fmaf(U[it], x, S[it]), q[it], acc);
                     S[it] = fmaf(w[it], S[it], x);
                 } else {
-                    S[it] = fmaf(af, S[it], x);
+                    S[it] = fmaf(MODE == 3 ? w[it] : af, S[it], x);
                     acc = fmaf(S[it], q[it], acc);
                 }
             }
@@ -441,7 +453,7 @@ matrix_scan_kernel(const ScanArgs a, int TB) {
     }
     if (MODE == 1) {
         if (cb == 0 && threadIdx.x == 0) st[(long long)D * DV + D] = m;
-    } else if (hd == 0 && cb == 0 && a.shift_src) {
+    } else if (MODE == 0 && hd == 0 && cb == 0 && a.shift_src) {
         const T* last = (const T*)a.shift_src + (long long)(s1 - 1) * a.W;
         float* keep = a.state + (long long)a.seq_slot[b] * a.state_stride;
         for (int e = threadIdx.x; e < a.W; e += SCAN_THREADS) keep[e] = to_f32(last[e]);
@@ -497,7 +509,7 @@ extern "C" int cm_matrix_scan(int dt, int mode, const ScanArgs* args, int B, cud
     if (B <= 0 || a.rows <= 0) return CM_OK;
     if (a.D <= 0 || a.DV <= 0 || a.D > 1024) CM_REFUSE("matrix_scan: head sizes %d x %d (keys up to 1024)", a.D, a.DV);
     if (!a.raw) CM_REFUSE("matrix_scan: the float buffer for the heads' raw outputs is missing");
-    if (mode < 0 || mode > 2) CM_REFUSE("matrix_scan: mode %d", mode);
+    if (mode < 0 || mode > 3) CM_REFUSE("matrix_scan: mode %d", mode);
     // Channels per thread (a power of two from 2 to 32) and parts per column (a power of two up to 32): as many
     // channels as leave the grid with a block per SM.  The walk is bound by its latency per row, not by arithmetic,
     // so what counts is how many SMs walk at once (measured on B200, 2,048 rows, one sequence, 8 heads of 64 x 128 /
@@ -516,7 +528,7 @@ extern "C" int cm_matrix_scan(int dt, int mode, const ScanArgs* args, int B, cud
     if (ks > 32) CM_REFUSE("matrix_scan: heads of %d key channels (up to 1024)", a.D);
     a.KS = ks;
     const int cols = SCAN_THREADS / ks, real = cols - (mode == 1 ? 1 : 0);
-    const int row_floats = (mode == 0 ? 3 : 2) * ks * rpt + cols + 4 + SCAN_THREADS;
+    const int row_floats = (mode == 0 || mode == 3 ? 3 : 2) * ks * rpt + cols + 4 + SCAN_THREADS;
     int tb = 12288 / row_floats;                          // about 48 KB of staged rows
     tb = tb < 1 ? 1 : (tb > SCAN_MAX_ROWS ? SCAN_MAX_ROWS : tb);
     const size_t smem = (size_t)tb * row_floats * sizeof(float);
@@ -548,6 +560,8 @@ extern "C" int cm_matrix_scan(int dt, int mode, const ScanArgs* args, int B, cud
     else if (dt == DT_BF16 && mode == 1) { SCAN_RPT(bf16, 1); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<bf16, 1>, egrid, 128, 0, st, n); }
     else if (dt == DT_F32 && mode == 2) { SCAN_RPT(float, 2); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<float, 1>, egrid, 128, 0, st, n); }
     else if (dt == DT_BF16 && mode == 2) { SCAN_RPT(bf16, 2); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<bf16, 1>, egrid, 128, 0, st, n); }
+    else if (dt == DT_F32 && mode == 3) { SCAN_RPT(float, 3); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<float, 0>, egrid, 128, 0, st, n); }
+    else if (dt == DT_BF16 && mode == 3) { SCAN_RPT(bf16, 3); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<bf16, 0>, egrid, 128, 0, st, n); }
     else return CM_ERR_DTYPE;
 #undef SCAN_RPT
 #undef SCAN_LAUNCH

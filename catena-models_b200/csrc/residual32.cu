@@ -18,6 +18,7 @@
 struct ResidualTerm {
     const void* p;
     const int* index;      // null: piece j of row r is row r * per_row + j; else row index[r * per_row + j] (negative: none)
+    const float* weights;  // null, or a factor per piece: weights[r * per_row + j] (a routed feed-forward's weights on its experts' outputs)
     float scale;
     int per_row;
     int is_f32;
@@ -63,6 +64,25 @@ norm_f32in_kernel(T* __restrict__ y, const float* __restrict__ x, const float* _
     for (int c = threadIdx.x; c < H; c += R32_THREADS) yr[c] = from_f32<T>((row[c] * inv) * w[c]);
 }
 
+// sum_i scale_i * sum_j (weights_i[j]) term_i[row * per_row_i + j] at column c: the terms are added to each other in their order.
+template <typename T>
+__device__ __forceinline__ float terms_at(const ResidualTerms& terms, long long r, int H, int c) {
+    float add = 0.f;
+    for (int i = 0; i < terms.n; ++i) {
+        const ResidualTerm& t = terms.t[i];
+        float s = 0.f;
+        for (int j = 0; j < t.per_row; ++j) {
+            const long long piece = t.index ? t.index[r * t.per_row + j] : r * t.per_row + j;
+            if (piece >= 0) {
+                const float v = term_at<T>(t, piece * H + c);
+                s = t.weights ? fmaf(t.weights[r * t.per_row + j], v, s) : s + v;
+            }
+        }
+        add += t.scale * s;
+    }
+    return add;
+}
+
 // h += sum_i scale_i * sum_j term_i[row * per_row_i + j] (+ bias);  n = T(norm(h) * w) when n is given.
 // The terms are added to each other first, in their order, and their sum to h: x + (mixer + feed-forward).
 template <typename T>
@@ -78,17 +98,7 @@ residual_add_norm_kernel(float* __restrict__ h, T* __restrict__ n_out, ResidualT
     float* hr = h + r * H;
     float ss = 0.f;
     for (int c = threadIdx.x; c < H; c += R32_THREADS) {
-        float add = 0.f;
-        for (int i = 0; i < terms.n; ++i) {
-            const ResidualTerm& t = terms.t[i];
-            float s = 0.f;
-            for (int j = 0; j < t.per_row; ++j) {
-                const long long piece = t.index ? t.index[r * t.per_row + j] : r * t.per_row + j;
-                if (piece >= 0) s += term_at<T>(t, piece * H + c);
-            }
-            add += t.scale * s;
-        }
-        float v = hr[c] + add;
+        float v = hr[c] + terms_at<T>(terms, r, H, c);
         if (bias) v += bias[c];
         hr[c] = v;
         row[c] = v;
@@ -104,6 +114,44 @@ residual_add_norm_kernel(float* __restrict__ h, T* __restrict__ n_out, ResidualT
     ss = block_sum(ss, scratch);
     const float inv = 1.f / sqrtf(ss / (float)H + eps);
     for (int c = threadIdx.x; c < H; c += R32_THREADS) nr[c] = from_f32<T>((row[c] * inv) * w[c]);
+}
+
+// The norm behind the sum (a post-norm layer), optionally followed by an average over the depth of the stack:
+//   x = norm(h_scale * h + terms) * w
+//   without `hist`:  h <- x
+//   with `hist` [n_hist][rows][H] (entry j at hist + j * hist_stride): entry n_hist - 1 <- x, and
+//                    h <- sum over j < n_hist of coef[j] * entry j          (j ascending; the last entry is x itself)
+//   n_out <- T(h) when given: the rows as the next reader's products take them.
+template <typename T>
+__global__ void __launch_bounds__(R32_THREADS)
+postnorm_residual_kernel(float* __restrict__ h, T* __restrict__ n_out, ResidualTerms terms, float h_scale,
+                         const float* __restrict__ w, int H, float eps, float* __restrict__ hist, long long hist_stride,
+                         int n_hist, const float* __restrict__ coef) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
+    const long long r = blockIdx.x;
+    float* hr = h + r * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += R32_THREADS) {
+        const float v = fmaf(h_scale, hr[c], terms_at<T>(terms, r, H, c));
+        row[c] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += R32_THREADS) {     // every thread reads back what it stored itself
+        float x = (row[c] * inv) * w[c];
+        if (hist) {
+            hist[(long long)(n_hist - 1) * hist_stride + r * H + c] = x;
+            float mix = 0.f;
+            for (int j = 0; j + 1 < n_hist; ++j) mix = fmaf(coef[j], hist[(long long)j * hist_stride + r * H + c], mix);
+            x = fmaf(coef[n_hist - 1], x, mix);
+        }
+        hr[c] = x;
+        if (n_out) n_out[r * H + c] = from_f32<T>(x);
+    }
 }
 
 // out[r] = T([a[r]; b[r]]) for float rows a and b of width H: the input of a projection over both.
@@ -144,11 +192,27 @@ extern "C" int cm_norm_f32in(int dt, void* y, const float* x, const float* w, in
     return CM_OK;
 }
 
-// terms: n_terms entries of (pointer, scale, pieces per row, stored as float?, index of the pieces or null) in parallel arrays.
+static void fill_terms(ResidualTerms& terms, int n_terms, const void* const* term_ptr, const float* term_scale,
+                       const int* term_per_row, const int* term_is_f32, const int* const* term_index,
+                       const float* const* term_weights) {
+    terms.n = n_terms;
+    for (int i = 0; i < R32_MAX_TERMS; ++i) {
+        terms.t[i].p = i < n_terms ? term_ptr[i] : nullptr;
+        terms.t[i].index = i < n_terms ? term_index[i] : nullptr;
+        terms.t[i].weights = i < n_terms ? term_weights[i] : nullptr;
+        terms.t[i].scale = i < n_terms ? term_scale[i] : 0.f;
+        terms.t[i].per_row = i < n_terms ? term_per_row[i] : 0;
+        terms.t[i].is_f32 = i < n_terms ? term_is_f32[i] : 0;
+    }
+}
+
+// terms: n_terms entries of (pointer, scale, pieces per row, stored as float?, index of the pieces or null, a weight per
+// piece or null) in parallel arrays.
 extern "C" int cm_residual_add_norm(int dt, float* h, void* n_out, int n_terms, const void* const* term_ptr,
                                     const float* term_scale, const int* term_per_row, const int* term_is_f32,
-                                    const int* const* term_index, const float* bias, const float* w, int rows, int H, float eps,
-                                    int kind, const float* alpha, const float* shift, cudaStream_t st) {
+                                    const int* const* term_index, const float* const* term_weights, const float* bias,
+                                    const float* w, int rows, int H, float eps, int kind, const float* alpha,
+                                    const float* shift, cudaStream_t st) {
     if (rows <= 0) return CM_OK;
     if (n_terms < 0 || n_terms > R32_MAX_TERMS) CM_REFUSE("residual_add_norm: %d terms (at most %d)", n_terms, R32_MAX_TERMS);
     if (n_out && !w) CM_REFUSE("residual_add_norm: a norm needs its weight");
@@ -156,20 +220,41 @@ extern "C" int cm_residual_add_norm(int dt, float* h, void* n_out, int n_terms, 
     size_t smem;
     if (row_smem(H, &smem) != CM_OK) return CM_ERR_SHAPE;
     ResidualTerms terms;
-    terms.n = n_terms;
-    for (int i = 0; i < R32_MAX_TERMS; ++i) {
-        terms.t[i].p = i < n_terms ? term_ptr[i] : nullptr;
-        terms.t[i].index = i < n_terms ? term_index[i] : nullptr;
-        terms.t[i].scale = i < n_terms ? term_scale[i] : 0.f;
-        terms.t[i].per_row = i < n_terms ? term_per_row[i] : 0;
-        terms.t[i].is_f32 = i < n_terms ? term_is_f32[i] : 0;
-    }
+    fill_terms(terms, n_terms, term_ptr, term_scale, term_per_row, term_is_f32, term_index, term_weights);
     if (dt == DT_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(residual_add_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         cm_launch(residual_add_norm_kernel<float>, rows, R32_THREADS, smem, st, h, (float*)n_out, terms, bias, w, H, eps, kind, alpha, shift);
     } else if (dt == DT_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(residual_add_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         cm_launch(residual_add_norm_kernel<bf16>, rows, R32_THREADS, smem, st, h, (bf16*)n_out, terms, bias, w, H, eps, kind, alpha, shift);
+    } else
+        return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+// The post-norm sum (postnorm_residual_kernel); terms as for cm_residual_add_norm.  coef: n_hist floats on the device.
+extern "C" int cm_postnorm_residual(int dt, float* h, void* n_out, int n_terms, const void* const* term_ptr,
+                                    const float* term_scale, const int* term_per_row, const int* term_is_f32,
+                                    const int* const* term_index, const float* const* term_weights, float h_scale,
+                                    const float* w, int rows, int H, float eps, float* hist, long long hist_stride,
+                                    int n_hist, const float* coef, cudaStream_t st) {
+    if (rows <= 0) return CM_OK;
+    if (n_terms < 0 || n_terms > R32_MAX_TERMS) CM_REFUSE("postnorm_residual: %d terms (at most %d)", n_terms, R32_MAX_TERMS);
+    if (!w) CM_REFUSE("postnorm_residual: the norm needs its weight");
+    if (hist && (n_hist < 1 || !coef)) CM_REFUSE("postnorm_residual: an average over %d entries needs its coefficients", n_hist);
+    size_t smem;
+    if (row_smem(H, &smem) != CM_OK) return CM_ERR_SHAPE;
+    ResidualTerms terms;
+    fill_terms(terms, n_terms, term_ptr, term_scale, term_per_row, term_is_f32, term_index, term_weights);
+    if (dt == DT_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(postnorm_residual_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cm_launch(postnorm_residual_kernel<float>, rows, R32_THREADS, smem, st, h, (float*)n_out, terms, h_scale, w, H, eps, hist,
+                  hist_stride, n_hist, coef);
+    } else if (dt == DT_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(postnorm_residual_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cm_launch(postnorm_residual_kernel<bf16>, rows, R32_THREADS, smem, st, h, (bf16*)n_out, terms, h_scale, w, H, eps, hist,
+                  hist_stride, n_hist, coef);
     } else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();

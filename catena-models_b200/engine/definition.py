@@ -47,9 +47,15 @@ class ModelDefinition:
     logit_softcap: float = 0.0       # logits <- cap * tanh(logits / cap) after the scale; 0: none
     residual_float32: bool = False   # the residual stream is float32 whatever the activation dtype (the blocks must take it)
     keep_embedding: bool = False     # a copy of the embedding rows stays in StepBatch.shared["embedding"] for the blocks
+    embedding_norm: object = None    # an RMS norm over every embedding row (a float32 stream), before the first block
+    # > 0: blocks average over the depth of the stack; the step keeps the stream before the first block and after every
+    # block in StepBatch.shared["depth_history"] (float32 [depth_entries, rows, width]); the model fills entry 0
+    depth_entries: int = 0
 
     def parts(self):
         out = list(self.blocks) + [self.final_norm]
+        if self.embedding_norm is not None:
+            out.append(self.embedding_norm)
         if self.head is not None:
             out.append(self.head)
         return out

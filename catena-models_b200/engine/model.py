@@ -30,6 +30,7 @@ class DecoderModel:
         self.fusable_decode = all(part.all_fused_decode_ok() for part in definition.parts())
         self.token_error = rt.token_error
         self.residual_dtype = torch.float32 if definition.residual_float32 else rt.dtype
+        self._one = None
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -93,6 +94,26 @@ class DecoderModel:
             with fuse:                     # the step's small products and residual sums run in few persistent launches
                 return self._forward(batch, cache)
 
+    def _prepare_stream(self, rt, batch, h, want_cast):
+        """The embedding norm (in place, float32) and entry 0 of the step's depth history; returns the stream rounded to
+        the activation dtype when the first block reads it without a norm of its own."""
+        d = self.definition
+        if h.dtype != torch.float32:
+            raise ValueError("an embedding norm or a depth average needs a float32 residual stream")
+        history = None
+        if d.depth_entries:
+            history = torch.empty((d.depth_entries, *h.shape), dtype=torch.float32, device=h.device)
+            batch.shared["depth_history"] = history
+        if d.embedding_norm is None:
+            history[0].copy_(h)
+            return h.to(rt.dtype) if want_cast and rt.dtype != torch.float32 else (h if want_cast else None)
+        if self._one is None:
+            self._one = torch.ones(1, dtype=torch.float32, device=h.device)
+        n_out = torch.empty(h.shape, dtype=rt.dtype, device=h.device) if want_cast and rt.dtype != torch.float32 else None
+        kernels.postnorm_residual(h, kernels.Terms(), 1.0, d.embedding_norm.weight, d.embedding_norm.eps, n_out=n_out,
+                                  history=None if history is None else history[:1], coef=None if history is None else self._one)
+        return n_out if n_out is not None else (h if want_cast else None)
+
     def _forward(self, batch, cache):
         rt = self.rt
         batch.shared.clear()
@@ -106,7 +127,12 @@ class DecoderModel:
             batch.shared["embedding"] = h.clone()          # blocks add to h in place; some read the embedding again
         plan = self.plan
         first_norm = self.blocks[plan[0].block].input_norm
-        n = first_norm.apply(rt, h) if first_norm is not None else None
+        n = None
+        d = self.definition
+        if d.embedding_norm is not None or d.depth_entries:
+            n = self._prepare_stream(rt, batch, h, first_norm is None)
+        if first_norm is not None:
+            n = first_norm.apply(rt, h)
         # when every row is wanted in order (a decode step), the last block's fused residual kernel
         # applies the final norm too and no rows need gathering
         whole = batch.wants_every_row and batch.n_want == batch.T
@@ -131,7 +157,6 @@ class DecoderModel:
             kernels.gather_rows(rows, h, batch.want_rows)
             normed = self.final_norm.apply(rt, rows)
             logits = rt.linear(normed, self.head_weight, out_dtype=torch.float32)
-        d = self.definition
         if d.logit_scale != 1.0 or d.logit_softcap > 0.0:
             kernels.scale_softcap(logits, d.logit_scale, d.logit_softcap)
         return logits

@@ -26,7 +26,7 @@ _SIGNATURES = {
     "cm_add_norm": [_i, _vp, _vp, _vp, _vp, _i, _ll, _vp, _vp, _vp, _i, _i, _f, _f, _vp],
     "cm_gemm_tc_few_rows_parts": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp],
     "cm_gemm_skinny_parts": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _ll, _i, _vp],
-    "cm_swiglu": [_i, _vp, _vp, _i, _i, _vp],
+    "cm_swiglu": [_i, _vp, _vp, _i, _i, _i, _vp],
     "cm_gather_rows": [_i, _vp, _vp, _vp, _i, _i, _vp],
     "cm_gemm_simt": [_i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
     "cm_gemm_skinny": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp],
@@ -54,20 +54,26 @@ _SIGNATURES = {
     "cm_zero_slots": [_vp, _i, _ll, _ll, ctypes.POINTER(ctypes.c_int), _i, _vp],
     "cm_copy_pages": [_vp, _vp, _vp, _i, _i, _ll, _ll, _vp],
     "cm_norm_f32in": [_i, _vp, _vp, _vp, _i, _i, _f, _i, _vp, _vp, _vp],
-    "cm_residual_add_norm": [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp, _vp, _vp],
+    "cm_residual_add_norm": [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp, _vp, _vp],
+    "cm_postnorm_residual": [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _vp, _i, _i, _f, _vp, _ll, _i, _vp, _vp],
     "cm_relu2_inplace": [_i, _vp, _ll, _vp],
     "cm_tap_rotate_store": [_i, _vp, _vp],
     "cm_diff_attn": [_i, _vp, _i, _i, _vp, _i, _vp],
     "cm_diff_attn_mma": [_vp, _i, _vp],
     "cm_concat_cast": [_i, _vp, _vp, _vp, _ll, _i, _vp],
     "cm_shift_mix": [_i, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _i, _ll, _i, _vp],
-    "cm_lowrank_decay": [_i, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
+    "cm_lowrank_decay": [_i, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _f, _vp],
     "cm_capped_gates": [_i, _vp, _vp, _vp, _vp, _f, _ll, _i, _i, _vp],
     "cm_tanh_inplace": [_i, _vp, _ll, _vp],
-    "cm_decay_from_logits": [_vp, _vp, _vp, _ll, _i, _vp],
+    "cm_decay_from_logits": [_vp, _vp, _vp, _ll, _i, _i, _f, _vp],
     "cm_matrix_scan": [_i, _i, _vp, _i, _vp],
     "cm_lightning_chunked": [_i, _vp, _i, _i, _vp, _vp],
-    "cm_moe_route": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _vp, _i, _vp],
+    "cm_moe_route": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _f, _f, _vp],
+    "cm_moe_identity": [_i, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
+    "cm_latent_prepare": [_i, _vp, _vp],
+    "cm_latent_query_turn": [_i, _vp, _vp],
+    "cm_latent_attn": [_i, _vp, _vp],
+    "cm_head_linear": [_i, _vp, _vp, _vp, _ll, _i, _i, _i, _ll, _ll, _i, _i, _i, _i, _vp],
     "cm_moe_gather": [_i, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
     "cm_gemm_tc_grouped": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _i, _vp, _vp],
     "cm_moe_grouped": [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
@@ -352,9 +358,10 @@ class PartialSums:
 
 
 class Terms(list):
-    """What a sublayer adds to a float32 residual stream: (tensor, factor, pieces per row[, index]) entries; the
-    tensor holds a row's pieces one below the other (rows * pieces rows), or anywhere, with `index` (int32
-    [rows * pieces], negative: no piece) saying where; float32 or the activation dtype (`residual_add_norm`)."""
+    """What a sublayer adds to a float32 residual stream: (tensor, factor, pieces per row[, index[, weights]])
+    entries; the tensor holds a row's pieces one below the other (rows * pieces rows), or anywhere, with `index`
+    (int32 [rows * pieces], negative: no piece) saying where; `weights` (float32 [rows * pieces]): a factor on
+    each piece; float32 or the activation dtype (`residual_add_norm`, `postnorm_residual`)."""
 
 
 def add_norm(h_out, n_out, m, h_in, w_post, w_next, eps_post, eps_next):
@@ -400,9 +407,10 @@ def scale_softcap(logits, scale=1.0, cap=0.0):
     _check(lib().cm_scale_softcap(_ptr(logits), logits.numel(), scale, cap, _stream()), "scale_softcap")
 
 
-def swiglu(out, gate_up):
+def swiglu(out, gate_up, gelu=False):
+    """out = act(gate) * up for the packed rows [gate | up]; act: silu, or the tanh form of gelu."""
     rows, F = out.shape
-    _check(lib().cm_swiglu(dtype_code(out.dtype), _ptr(out), _ptr(gate_up), rows, F, _stream()), "swiglu")
+    _check(lib().cm_swiglu(dtype_code(out.dtype), _ptr(out), _ptr(gate_up), rows, F, int(gelu), _stream()), "swiglu")
 
 
 def gather_rows(out, x, rows):
@@ -716,7 +724,7 @@ def scatter_i32(table, index, value, count, max_count):
 
 
 def copy_pages(pool, src, dst):
-    """pool: [layers, 2, pages, ...] paged storage of one group; page src[i] is copied to page dst[i]
+    """pool: [layers, planes, pages, ...] paged storage of one group; page src[i] is copied to page dst[i]
     in every layer and plane (int32 device tensors of equal length)."""
     n = src.numel()
     outer, pages = pool.shape[0] * pool.shape[1], pool.shape[2]
@@ -761,31 +769,64 @@ def relu2_inplace(x):
            cost=lambda: (f"{tuple(x.shape)}", 2 * _nbytes(x), 0))
 
 
-def residual_add_norm(h, terms, n_out=None, w_next=None, eps=0.0, bias=None, dyt=None):
-    """h (float32, in place) += sum over `terms` of scale * (the sum of a row's pieces) (+ bias, a float32
-    row); n_out = norm(h) * w_next in the activation dtype when given (`dyt` = (alpha, shift): a dynamic tanh,
-    as for `norm_f32in`).  A term is (tensor, scale, pieces per row) or (tensor, scale, pieces per row, index):
-    see `Terms`."""
-    rows, H = h.shape
-    if h.dtype != torch.float32 or not h.is_contiguous() or len(terms) > 4:
-        raise KernelError("residual_add_norm: a contiguous float32 stream and at most four terms")
-    terms = [tuple(t) + (None,) * (4 - len(t)) for t in terms]
-    act = n_out.dtype if n_out is not None else next((t[0].dtype for t in terms if t[0].dtype != torch.float32), torch.float32)
-    for t, _, per_row, index in terms:
+def _term_arrays(terms, rows, H, act, name):
+    """The parallel arrays that the residual kernels take for up to four terms."""
+    if len(terms) > 4:
+        raise KernelError(f"{name}: at most four terms")
+    terms = [tuple(t) + (None,) * (5 - len(t)) for t in terms]
+    for t, _, per_row, index, weights in terms:
         fits = t.numel() == rows * per_row * H if index is None else (index.numel() == rows * per_row and t.shape[-1] == H)
         if not t.is_contiguous() or not fits or t.dtype not in (torch.float32, act):
-            raise KernelError("residual_add_norm: a term's shape or dtype does not fit")
+            raise KernelError(f"{name}: a term's shape or dtype does not fit")
+        if weights is not None and (weights.dtype != torch.float32 or weights.numel() != rows * per_row):
+            raise KernelError(f"{name}: a term's weights are float32, one per piece")
     n = len(terms)
     ptrs = (ctypes.c_void_p * 4)(*[t[0].data_ptr() for t in terms], *([None] * (4 - n)))
     scales = (ctypes.c_float * 4)(*[float(t[1]) for t in terms], *([0.0] * (4 - n)))
     per = (ctypes.c_int * 4)(*[int(t[2]) for t in terms], *([0] * (4 - n)))
     f32 = (ctypes.c_int * 4)(*[int(t[0].dtype == torch.float32) for t in terms], *([0] * (4 - n)))
     index = (ctypes.c_void_p * 4)(*[_ptr(t[3]) for t in terms], *([None] * (4 - n)))
+    weights = (ctypes.c_void_p * 4)(*[_ptr(t[4]) for t in terms], *([None] * (4 - n)))
+    return terms, n, ptrs, scales, per, f32, index, weights
+
+
+def residual_add_norm(h, terms, n_out=None, w_next=None, eps=0.0, bias=None, dyt=None):
+    """h (float32, in place) += sum over `terms` of scale * (the sum of a row's pieces) (+ bias, a float32
+    row); n_out = norm(h) * w_next in the activation dtype when given (`dyt` = (alpha, shift): a dynamic tanh,
+    as for `norm_f32in`).  A term is (tensor, scale, pieces per row[, index[, weights]]): see `Terms`."""
+    rows, H = h.shape
+    if h.dtype != torch.float32 or not h.is_contiguous():
+        raise KernelError("residual_add_norm: a contiguous float32 stream")
+    act = n_out.dtype if n_out is not None else next((t[0].dtype for t in terms if t[0].dtype != torch.float32), torch.float32)
+    terms, n, ptrs, scales, per, f32, index, weights = _term_arrays(terms, rows, H, act, "residual_add_norm")
     kind, alpha, shift = (NORM_DYT, dyt[0], dyt[1]) if dyt is not None else (NORM_RMS, None, None)
-    _check(lib().cm_residual_add_norm(dtype_code(act), _ptr(h), _ptr(n_out), n, ptrs, scales, per, f32, index, _ptr(bias),
+    _check(lib().cm_residual_add_norm(dtype_code(act), _ptr(h), _ptr(n_out), n, ptrs, scales, per, f32, index, weights, _ptr(bias),
                                       _ptr(w_next), rows, H, eps, kind, _ptr(alpha), _ptr(shift), _stream()), "residual_add_norm",
            cost=lambda: (f"{rows}x{H}, {n} terms", 2 * _nbytes(h) + _nbytes(n_out) + sum(rows * t[2] * H * t[0].element_size() for t in terms),
                          (n + 5) * rows * H))
+
+
+def postnorm_residual(h, terms, h_scale, w, eps, n_out=None, history=None, coef=None):
+    """The norm behind the sum: x = norm(h_scale * h + terms) * w (w float32 [H]; a norm with one number has it
+    repeated), float32.  Without `history`, h <- x.  With `history` (float32 [n, rows, H], contiguous: what the stack
+    held before each layer so far, entry n - 1 free) and `coef` (float32 [n] on the device): entry n - 1 <- x and
+    h <- sum_j coef[j] * entry j.  n_out (activation dtype, optional) <- h, for the next reader's products."""
+    rows, H = h.shape
+    if h.dtype != torch.float32 or not h.is_contiguous():
+        raise KernelError("postnorm_residual: a contiguous float32 stream")
+    act = n_out.dtype if n_out is not None else next((t[0].dtype for t in terms if t[0].dtype != torch.float32), torch.float32)
+    terms, n, ptrs, scales, per, f32, index, weights = _term_arrays(terms, rows, H, act, "postnorm_residual")
+    n_hist, stride = 0, 0
+    if history is not None:
+        n_hist, stride = history.shape[0], history.stride(0)
+        if (history.dtype != torch.float32 or tuple(history.shape[1:]) != (rows, H) or not history[0].is_contiguous()
+                or coef is None or coef.dtype != torch.float32 or coef.numel() != n_hist):
+            raise KernelError("postnorm_residual: history float32 [n, rows, H] with n float32 coefficients")
+    _check(lib().cm_postnorm_residual(dtype_code(act), _ptr(h), _ptr(n_out), n, ptrs, scales, per, f32, index, weights,
+                                      float(h_scale), _ptr(w), rows, H, eps, _ptr(history), stride, n_hist, _ptr(coef), _stream()),
+           "postnorm_residual",
+           cost=lambda: (f"{rows}x{H}, {n} terms, depth {n_hist}", 2 * _nbytes(h) + _nbytes(n_out) + (n_hist + 1) * rows * H * 4
+                         + sum(rows * t[2] * H * t[0].element_size() for t in terms), (n + 5 + 2 * n_hist) * rows * H))
 
 
 def concat_cast(out, a, b):
@@ -805,14 +846,15 @@ def shift_mix(out, h, mu, state, tok_seq, tok_pos, seq_pos0, seq_slot):
            "shift_mix", cost=lambda: (f"{S}x{rows}x{W}", _nbytes(h, out, mu), 2 * S * rows * W))
 
 
-def lowrank_decay(out, x, w1, w2, w0):
-    """out = exp(-exp(W2 tanh(W1 x) + w0)) in float32: x [rows, W], W1 [R, W], w2 = W2 transposed [R, C], w0 [C]."""
+def lowrank_decay(out, x, w1, w2, w0, tau=None):
+    """out = exp(-exp(W2 tanh(W1 x) + w0)) in float32: x [rows, W], W1 [R, W], w2 = W2 transposed [R, C], w0 [C].
+    With `tau`: out = sigmoid(W2 (W1 x) + w0)^(1/tau) instead (no activation between the two products)."""
     rows, W = x.shape
     R, C = w1.shape[0], w2.shape[1]
     if w1.dtype != x.dtype or w2.dtype != x.dtype or not (x.is_contiguous() and w1.is_contiguous() and w2.is_contiguous()):
         raise KernelError("lowrank_decay: contiguous operands of one dtype")
     _check(lib().cm_lowrank_decay(dtype_code(x.dtype), _ptr(out), _ptr(x), _ptr(w1), _ptr(w2), _ptr(w0), rows, W, R, C,
-                                  _stream()), "lowrank_decay",
+                                  int(tau is not None), float(tau or 0.0), _stream()), "lowrank_decay",
            cost=lambda: (f"{rows}x{W} rank {R} -> {C}", _nbytes(x, out, w1, w2), 2 * rows * R * (W + C)))
 
 
@@ -822,10 +864,11 @@ def tanh_inplace(x):
            cost=lambda: (f"{tuple(x.shape)}", 2 * _nbytes(x), 0))
 
 
-def decay_from_logits(out, z, w0):
-    """out = exp(-exp(z + w0)): z, out float32 [rows, C] contiguous, w0 float32 [C]."""
+def decay_from_logits(out, z, w0, tau=None):
+    """out = exp(-exp(z + w0)), or sigmoid(z + w0)^(1/tau) with `tau`: z, out float32 [rows, C] contiguous, w0 float32 [C]."""
     rows, C = z.shape
-    _check(lib().cm_decay_from_logits(_ptr(out), _ptr(z), _ptr(w0), rows, C, _stream()), "decay_from_logits",
+    _check(lib().cm_decay_from_logits(_ptr(out), _ptr(z), _ptr(w0), rows, C, int(tau is not None), float(tau or 0.0), _stream()),
+           "decay_from_logits",
            cost=lambda: (f"{rows}x{C}", _nbytes(z, out), 0))
 
 
@@ -856,6 +899,7 @@ def matrix_scan(mode, out, q, k, v, g, decay, bonus, norm_w, state, state_offset
     S <- diag(decay_t) S + k v^T (decay float32 [rows, H D]; gate silu(g)).  mode "memory": log-domain
     gates with a running maximum and a normaliser (decay float32 [rows, 2 H]: i, then f; gate sigmoid(g)).
     mode "constant": S <- w S + k v^T, o = S^T q with one decay per head (decay float32 [H]; gate sigmoid(g));
+    mode "gated": S <- diag(decay_t) S + k v^T, o = S^T q (decay float32 [rows, H D]; gate silu(g)).
     `qkv_silu`: q, k and v pass through silu as they are read.  `norm_all_heads`: the unit norm runs over all
     heads of a row together.  `chunk_scratch` (mode "constant"; float32, at least `lightning_scratch_floats` elements for
     sequences of up to `max_len` rows): the prompt form, which regroups the sums into chunks of 64 rows so that only the
@@ -884,7 +928,7 @@ def matrix_scan(mode, out, q, k, v, g, decay, bonus, norm_w, state, state_offset
                cost=lambda: (f"{B} sequences, {rows} rows, {H} heads of {D}x{DV}", _nbytes(q, k, v, g, out) + 2 * B * H * D * DV * 4,
                              6 * rows * H * D * DV))
         return
-    _check(lib().cm_matrix_scan(dtype_code(out.dtype), {"decay": 0, "memory": 1, "constant": 2}[mode], ctypes.byref(a), B, _stream()),
+    _check(lib().cm_matrix_scan(dtype_code(out.dtype), {"decay": 0, "memory": 1, "constant": 2, "gated": 3}[mode], ctypes.byref(a), B, _stream()),
            "matrix_scan_" + mode, 2,
            cost=lambda: (f"{B} sequences, {rows} rows, {H} heads of {D}x{DV}",
                          _nbytes(q, k, v, g, out) + (0 if decay is None or decay.dim() < 2 else rows * decay.shape[1] * 4) + 2 * B * H * D * DV * 4,
@@ -1022,6 +1066,102 @@ def _diff_attn_cost(batch, T, H, G, D, DV, window, keep, esz, rows_form):
             2 * 2 * T * seen * H * (D + DV))
 
 
+# ------------------------------------------------------------------ latent attention
+class _LatentArgs(ctypes.Structure):
+    """csrc/latent.h: LatentArgs."""
+    _fields_ = [("proj", _vp), ("ld_proj", _ll), ("q_off", _i), ("kv_off", _i), ("cq", _vp), ("wq_norm", _vp), ("wkv_norm", _vp),
+                ("rate", _vp), ("q", _vp), ("ldq", _ll), ("qa", _vp), ("ldqa", _ll), ("gate", _vp), ("ld_gate", _ll),
+                ("out", _vp), ("ldo", _ll), ("H", _i), ("D", _i), ("R", _i), ("KR", _i), ("QR", _i), ("E", _i), ("EC", _i),
+                ("eps", _f), ("scale", _f), ("rows", _ll), ("tok_pos", _vp), ("tok_seq", _vp), ("seq_start", _vp),
+                ("seq_pos0", _vp), ("seq_end", _vp), ("seq_slot", _vp), ("pool", _vp), ("ptab", _vp), ("ptab_stride", _ll),
+                ("B", _i), ("max_len", _i), ("splits", _i), ("chunk", _i), ("parts", _vp)]
+
+
+LATENT_KEY_TILE = 32               # csrc/latent.cu: cache entries of a key tile; a split's keys are a multiple of it
+
+
+def latent_entry_size(kv_rank, rot_dim):
+    """Channels of a cache entry of the latent attention: the latent, the turned key part, zeros up to a multiple of 8."""
+    return -(-(kv_rank + rot_dim) // 8) * 8
+
+
+def _latent_args(batch, pool, ptab, H, D, R, KR, QR, eps=0.0, scale=1.0, **fields):
+    return _LatentArgs(H=H, D=D, R=R, KR=KR, QR=QR, E=KR + R, EC=pool.shape[-1], eps=eps, scale=scale, rows=batch.T,
+                       tok_pos=_ptr(batch.tok_pos), tok_seq=_ptr(batch.tok_seq), seq_start=_ptr(batch.seq_start),
+                       seq_pos0=_ptr(batch.seq_pos0), seq_end=_ptr(batch.seq_end), seq_slot=_ptr(batch.seq_slot),
+                       pool=_ptr(pool), ptab=_ptr(ptab), ptab_stride=ptab.stride(0), B=batch.B, max_len=batch.max_len,
+                       splits=1, chunk=0, **fields)
+
+
+def latent_prepare(cq, proj, q_off, kv_off, wq_norm, wkv_norm, rate, pool, ptab, batch, H, D, R, KR, QR, eps):
+    """Per row of the step: cq = norm(proj[q_off : q_off + QR]) * wq_norm (activation dtype, for the product that
+    makes the heads' queries), and the row's cache entry [norm(proj[kv_off : kv_off + KR]) * wkv_norm | the next R
+    channels turned by the position (pairs 2i, 2i + 1 by position * rate[i]) | zeros] into pool [pages, PAGE_TOKENS, EC]
+    through the page table.  Norms and angles are float32."""
+    a = _latent_args(batch, pool, ptab, H, D, R, KR, QR, eps=eps, proj=_ptr(proj), ld_proj=proj.stride(0), q_off=q_off,
+                     kv_off=kv_off, cq=_ptr(cq), wq_norm=_ptr(wq_norm), wkv_norm=_ptr(wkv_norm), rate=_ptr(rate))
+    if proj.stride(1) != 1 or not cq.is_contiguous() or cq.dtype != proj.dtype or pool.dtype != proj.dtype:
+        raise KernelError("latent_prepare: row-major operands of one dtype")
+    _check(lib().cm_latent_prepare(dtype_code(proj.dtype), ctypes.byref(a), _stream()), "latent_prepare",
+           cost=lambda: (f"{batch.T} rows, {QR} + {KR} + {R}", batch.T * (2 * QR + 2 * (KR + R)) * proj.element_size(), 6 * batch.T * (QR + KR)))
+
+
+def latent_query_turn(qa, q, rate, pool, ptab, batch, H, D, R, KR):
+    """qa[t, h, KR:KR + R] (float32) = the last R channels of head h's query q[t, h, :D + R], turned by the position."""
+    a = _latent_args(batch, pool, ptab, H, D, R, KR, 0, q=_ptr(q), ldq=q.stride(0), qa=_ptr(qa), ldqa=qa.stride(0), rate=_ptr(rate))
+    if qa.dtype != torch.float32 or qa.stride(1) != 1 or q.stride(1) != 1:
+        raise KernelError("latent_query_turn: float32 rows for the turned queries")
+    _check(lib().cm_latent_query_turn(dtype_code(q.dtype), ctypes.byref(a), _stream()), "latent_query_turn",
+           cost=lambda: (f"{batch.T} rows, {H} heads of {R}", batch.T * H * R * (4 + q.element_size()), 6 * batch.T * H * R))
+
+
+def latent_attn_splits(rows, H, keys, sm_count=148):
+    """(splits, keys per split) for a step of `rows` single-token rows over up to `keys` cache entries: enough blocks
+    to fill the device, a split at least four key tiles long."""
+    blocks = -(-rows * H // 32)
+    tiles = -(-keys // LATENT_KEY_TILE)
+    splits = max(1, min(tiles // 4, -(-sm_count // blocks)))
+    chunk = -(-tiles // splits) * LATENT_KEY_TILE
+    return -(-keys // chunk) if splits > 1 else 1, chunk
+
+
+def latent_attn(out, qa, gate, pool, ptab, batch, H, R, KR, scale, splits=1, chunk=0, parts=None):
+    """Causal softmax attention of every head's query row qa [rows, H, KR + R] (float32) over the cache entries of
+    its sequence (positions <= the row's own); out [rows, H, KR] (float32) = the weights' sum over the latents,
+    times sigmoid(gate[t, h]) when `gate` ([rows, >= H] logits, activation dtype) is given.  `splits` > 1: the keys
+    are cut into runs of `chunk` entries, each run a block of its own, merged afterwards (`parts`: float32 scratch of
+    rows * H * splits * (2 + KR))."""
+    a = _latent_args(batch, pool, ptab, H, 0, R, KR, 0, scale=scale, qa=_ptr(qa), ldqa=qa.stride(0), gate=_ptr(gate),
+                     ld_gate=0 if gate is None else gate.stride(0), out=_ptr(out), ldo=out.stride(0))
+    a.splits, a.chunk, a.parts = splits, chunk, _ptr(parts)
+    if qa.dtype != torch.float32 or out.dtype != torch.float32 or (gate is not None and gate.dtype != pool.dtype):
+        raise KernelError("latent_attn: float32 queries and sums")
+    if splits > 1 and (parts is None or parts.numel() < batch.T * H * splits * (2 + KR)):
+        raise KernelError("latent_attn: the splits' scratch is missing or short")
+    keys = batch.max_end
+    _check(lib().cm_latent_attn(dtype_code(pool.dtype), ctypes.byref(a), _stream()), "latent_attn", 2 if splits > 1 else 1,
+           cost=lambda: (f"{batch.B} sequences, {batch.T} rows, {H} heads over {KR}+{R}",
+                         _nbytes(qa, out) + sum((p + n) * pool.shape[-1] * pool.element_size() for p, n in zip(batch.positions, batch.lengths)),
+                         sum(2 * n * H * (p + (n + 1) // 2) * (2 * KR + R) for p, n in zip(batch.positions, batch.lengths))))
+
+
+def head_linear(y, x, w, H, x_size, y_size):
+    """A matrix per head: y[t, h * y_size + n] = sum_k x[t, h * x_size + k] * w[h, n, k] for w [H, N, K].  x and y are
+    in w's dtype or float32 (a sum that stays unrounded between two steps)."""
+    rows = x.shape[0]
+    N, K = w.shape[1], w.shape[2]
+    if x.stride(1) != 1 or y.stride(1) != 1 or not w.is_contiguous() or w.shape[0] != H:
+        raise KernelError("head_linear: row-major operands, one matrix per head")
+    for t in (x, y):
+        if t.dtype not in (w.dtype, torch.float32):
+            raise KernelError("head_linear: rows in the matrices' dtype or float32")
+    _check(lib().cm_head_linear(dtype_code(w.dtype), _ptr(y), _ptr(x), _ptr(w), rows, H, N, K, x.stride(0), y.stride(0), x_size,
+                                y_size, int(x.dtype == torch.float32 and w.dtype != torch.float32),
+                                int(y.dtype == torch.float32 and w.dtype != torch.float32), _stream()), "head_linear",
+           cost=lambda: (f"{rows} rows, {H} heads of {N}x{K}", rows * H * (N * y.element_size() + K * x.element_size()) + _nbytes(w),
+                         2 * rows * H * N * K))
+
+
 # ------------------------------------------------------------------ routed feed-forward
 MOE_TILE_SIMT, MOE_TILE_TC = 32, 128     # rows of a row tile: the CUDA-core grouped products, the tcgen05 grouped product
 
@@ -1044,21 +1184,39 @@ def moe_tile_group(work, pairs, experts, tile_rows):
 
 
 def moe_route(ids, wts, perm, dest, work, h, w_router, tok_seq, top, softmax_gate=False, renormalize=False,
-              tile_rows=MOE_TILE_SIMT, xs=None, apply_weight=False):
+              tile_rows=MOE_TILE_SIMT, xs=None, apply_weight=False, correction=None, groups=0, keep=0, identity=0, scale=1.0,
+              renorm_eps=0.0):
     """Scores of every token's experts in float32 (sigmoid, or softmax over the experts), the `top` best
     (ids, wts: [rows * top]; -1 for rows of padding), and the pairs in the order of their experts, every expert's
     rows beginning a row tile of `tile_rows` rows: perm[sorted row] = pair (moe_max_tiles * tile_rows entries),
     dest[pair] = sorted row (-1: none), the list of row tiles in `work` (int32, moe_work_size entries).  With `xs`
     ([moe_max_tiles * tile_rows, W]) the experts' inputs are gathered into it in the same call (`moe_gather`).  A step of
-    up to 64 rows runs all of this in one launch of one block."""
+    up to 64 rows runs all of this in one launch of one block.
+    `correction` (float32 [E]): added to the scores for the choice only.  `groups`, `keep`: the experts form `groups` equal
+    groups of neighbours, and only experts of the `keep` groups with the largest best choice score can be chosen.
+    `identity`: the last `identity` router outputs are experts without matrices whose output is their input: their pairs get
+    a weight and dest -1 (`moe_identity` adds them).  `scale`: a factor on the weights; `renorm_eps`: added to the sum that
+    `renormalize` divides by."""
     rows, W = h.shape
     E = w_router.shape[0]
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != E):
+        raise KernelError("moe_route: one float32 correction per router output")
     if w_router.dtype != h.dtype or not (h.is_contiguous() and w_router.is_contiguous()):
         raise KernelError("moe_route: contiguous operands of one dtype")
     _check(lib().cm_moe_route(dtype_code(h.dtype), _ptr(ids), _ptr(wts), _ptr(perm), _ptr(dest), _ptr(work), _ptr(h),
                               _ptr(w_router), _ptr(tok_seq), rows, W, E, top, int(softmax_gate), int(renormalize), tile_rows,
-                              _ptr(xs), int(apply_weight), _stream()), "moe_route", 1 if rows <= 64 and rows * E <= 8192 else (4 if xs is not None else 3),
+                              _ptr(xs), int(apply_weight), _ptr(correction), int(groups), int(keep), int(identity), float(scale),
+                              float(renorm_eps), _stream()), "moe_route",
+           1 if rows <= 64 and rows * E * (2 if correction is not None or groups else 1) <= 8192 else (4 if xs is not None else 3),
            cost=lambda: (f"{rows}x{W} over {E}, top {top}", _nbytes(h, w_router), 2 * rows * E * W))
+
+
+def moe_identity(y, h, ids, wts, top, real):
+    """y[t] (float32) = h[t] times the sum of the weights of token t's pairs whose expert is an identity expert
+    (id >= real)."""
+    rows, K = h.shape
+    _check(lib().cm_moe_identity(dtype_code(h.dtype), _ptr(y), _ptr(h), _ptr(ids), _ptr(wts), rows, top, real, K, _stream()),
+           "moe_identity", cost=lambda: (f"{rows}x{K}", _nbytes(h, y), rows * K))
 
 
 def moe_gather(xs, h, dest, wts, top, apply_weight):

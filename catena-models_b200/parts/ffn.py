@@ -1,4 +1,4 @@
-"""SwiGLU feed-forward: a = (g * sigmoid(g)) * u with g = x Wgate^T, u = x Wup^T, then Wdown
+"""Gated feed-forward: a = act(g) * u with g = x Wgate^T, u = x Wup^T, then Wdown; act is silu (SwiGLU) or tanh-gelu
 (src/catena/lfm3.hex:833-845; fused epilogue src/catena/lfm3_wmma.hex:10790-10815).  Gate and up
 are packed into one matrix at bind time so that one product reads x once
 (src/lfm3.rs:1062-1075 fuses them in its kernel the same way).
@@ -14,10 +14,16 @@ class SwiGLU(FeedForward):
     fused_decode_ok = True
     supports_append = True
 
-    def __init__(self, prefix, hidden, intermediate, names=None, out_dtype=None):
-        """out_dtype "float32": the down projection's result stays in float (for a float residual stream)."""
+    def __init__(self, prefix, hidden, intermediate, names=None, out_dtype=None, activation="silu"):
+        """out_dtype "float32": the down projection's result stays in float (for a float residual stream).
+        activation: what the gate passes through, "silu" or "gelu_tanh" (the tanh form of gelu)."""
         import torch
 
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError("SwiGLU: activation silu|gelu_tanh")
+        self.gelu = activation == "gelu_tanh"
+        if self.gelu:
+            self.fused_decode_ok = False         # the products' fused silu epilogue is not this activation
         self.out_dtype = {None: None, "float32": torch.float32}[out_dtype]
         names = names or {}
         n = lambda key, default: prefix + names.get(key, default)
@@ -30,7 +36,14 @@ class SwiGLU(FeedForward):
         return [self.gate_up, self.down]
 
     def forward(self, rt, batch, x):
-        a = rt.gate_up_swiglu(x, self.gate_up.weight, self.intermediate)
+        if self.gelu:
+            from .. import kernels
+            import torch
+
+            a = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
+            kernels.swiglu(a, self.gate_up.apply(rt, x), gelu=True)
+        else:
+            a = rt.gate_up_swiglu(x, self.gate_up.weight, self.intermediate)
         return self.down.apply(rt, a, out_dtype=self.out_dtype, partial_ok=batch.partial_sums_ok and self.out_dtype is None)
 
 

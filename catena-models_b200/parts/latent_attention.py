@@ -1,0 +1,120 @@
+"""Attention whose keys and values are read out of one small latent row per token (multi-head latent attention).
+
+Per token, from the mixer's input h (one product over the packed rows [W_dq; W_dkv; W_g]):
+
+    c_q = rms(W_dq h) * w_q                      the query latent (q_rank channels)
+    [c' | r] = W_dkv h ;  c = rms(c') * w_kv     the latent (kv_rank channels); r: rot_dim channels, not normed
+    r <- turn(r, position)                       one turned key part that all heads share
+    g = W_g h                                    one gate logit per head
+
+and per head, with q = [q_plain (dim) | q_turn (rot_dim)] = W_uq c_q, q_turn turned by the position:
+
+    score(i, j) = (q_plain_i . (W_uk c_j) + q_turn_i . r_j) * scale,   j <= i,   softmax over j
+    o_i = (sum_j p_ij W_uv c_j) * sigmoid(g_i)
+
+then the output projection over the concatenated heads.  Only [c | r] is cached: one row of kv_rank + rot_dim
+channels per token whatever the number of heads (`KVStateSpec(..., planes=1)`).  The kernels never form the heads'
+keys and values: W_uk is moved to the query side (a head's query against the cache is [W_uk^T q_plain | q_turn]) and
+W_uv behind the weighted sum over the latents, each a product with one matrix per head (`kernels.head_linear`).
+Norms, angles, scores, softmax and the sums over the latents are float32.
+
+The position encoding turns the leading `position.dims` channels of the rot_dim part in interleaved pairs; further
+channels of that part pass unchanged.
+
+Every kind of step (whole prompts, portions, single tokens, mixed lengths) writes its entries to the cache first and
+then reads all keys from there, so they agree.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..cache.spec import KVStateSpec
+from ..weights.loader import TensorSpec
+from .base import Mixer, register_part
+from .linear import Linear
+
+
+class LatentAttention(Mixer):
+    prompt_capturable = True
+    supports_append = True
+
+    def __init__(self, prefix, hidden, heads, dim, rot_dim, value_dim, kv_rank, q_rank, position, scale, eps,
+                 output_gate=True, out_dtype=None):
+        if min(heads, dim, value_dim, kv_rank, q_rank) < 1 or rot_dim < 0:
+            raise ValueError("LatentAttention: sizes must be positive")
+        if getattr(position, "dims", 0) and position.pairing != "interleaved":
+            raise ValueError("LatentAttention: the turned part is paired 2i with 2i + 1")
+        self.prefix, self.hidden = prefix, hidden
+        self.heads, self.dim, self.rot_dim, self.value_dim = heads, dim, rot_dim, value_dim
+        self.kv_rank, self.q_rank = kv_rank, q_rank
+        self.position, self.scale, self.eps = position, float(scale), float(eps)
+        self.output_gate = bool(output_gate)
+        self.out_dtype = {None: None, "float32": torch.float32}[out_dtype]
+        self.entry = kernels.latent_entry_size(kv_rank, rot_dim)
+        names, rows = [prefix + "dq", prefix + "dkv"], [q_rank, kv_rank + rot_dim]
+        if self.output_gate:
+            names.append(prefix + "g")
+            rows.append(heads)
+        self.down = Linear(names, rows, hidden)
+        self.up_q = Linear(prefix + "uq", heads * (dim + rot_dim), q_rank)
+        self.out = Linear(prefix + "o", hidden, heads * value_dim)
+        self.wq_norm = self.wkv_norm = self.w_uk_t = self.w_uv = self.rate = None
+
+    def children(self):
+        return [self.down, self.up_q, self.out, self.position]
+
+    def tensor_specs(self):
+        p = self.prefix
+        return [TensorSpec(p + "dq.norm", (self.q_rank,), "norm"), TensorSpec(p + "dkv.norm", (self.kv_rank,), "norm"),
+                TensorSpec(p + "uk", (self.heads * self.dim, self.kv_rank)),
+                TensorSpec(p + "uv", (self.heads * self.value_dim, self.kv_rank))]
+
+    def bind(self, tensors, rt):
+        p, H = self.prefix, self.heads
+        self.wq_norm = tensors[p + "dq.norm"].to(torch.float32).contiguous()
+        self.wkv_norm = tensors[p + "dkv.norm"].to(torch.float32).contiguous()
+        # W_uk^T per head [H, kv_rank, dim]: the query side's product; W_uv per head [H, value_dim, kv_rank]
+        self.w_uk_t = tensors[p + "uk"].view(H, self.dim, self.kv_rank).transpose(1, 2).contiguous()
+        self.w_uv = tensors[p + "uv"].view(H, self.value_dim, self.kv_rank).contiguous()
+        # a rate per pair of the turned part; pairs that the position encoding does not cover stay (rate 0)
+        rate = torch.zeros(max(1, (self.rot_dim + 1) // 2), dtype=torch.float32, device=self.w_uv.device)
+        table = self.position.rate_table()
+        if table is not None:
+            n = min(table.numel(), self.rot_dim // 2)
+            rate[:n] = table[:n]
+        self.rate = rate
+        self._bound = [self.wq_norm, self.wkv_norm, self.w_uk_t, self.w_uv]
+
+    def state_spec(self):
+        return KVStateSpec(1, self.entry, 0, planes=1)
+
+    def forward(self, rt, batch, x, state):
+        H, D, R, DV, KR, QR = self.heads, self.dim, self.rot_dim, self.value_dim, self.kv_rank, self.q_rank
+        T, dev = batch.T, x.device
+        pool, ptab = state.pool, state.ptab
+        proj = self.down.apply(rt, x)                                   # [T, QR + KR + R (+ H)]
+        cq = torch.empty((T, QR), dtype=x.dtype, device=dev)
+        kernels.latent_prepare(cq, proj, 0, QR, self.wq_norm, self.wkv_norm, self.rate, pool, ptab, batch, H, D, R, KR, QR,
+                               self.eps)
+        q = self.up_q.apply(rt, cq)                                      # [T, H (D + R)]
+        qa = torch.empty((T, H * (KR + R)), dtype=torch.float32, device=dev)
+        kernels.head_linear(qa, q, self.w_uk_t, H, D + R, KR + R)
+        if R:
+            kernels.latent_query_turn(qa, q, self.rate, pool, ptab, batch, H, D, R, KR)
+        sums = torch.empty((T, H * KR), dtype=torch.float32, device=dev)
+        splits, chunk, parts = 1, 0, None
+        if batch.kind == "decode":
+            # sized by the longest sequence that the step's class of lengths allows, so that a recording serves the class
+            keys = state.spec.entries(state.spec.length_class(batch.max_end))
+            splits, chunk = kernels.latent_attn_splits(T, H, keys)
+            if splits > 1:
+                parts = rt.scratch("latent_attn_parts", T * H * splits * (2 + KR))
+        kernels.latent_attn(sums, qa, proj[:, QR + KR + R:] if self.output_gate else None, pool, ptab, batch, H, R, KR,
+                            self.scale, splits=splits, chunk=chunk, parts=parts)
+        ctx = torch.empty((T, H * DV), dtype=x.dtype, device=dev)
+        kernels.head_linear(ctx, sums, self.w_uv, H, KR, DV)
+        return self.out.apply(rt, ctx, out_dtype=self.out_dtype)
+
+
+register_part("mixer", "latent_attention", LatentAttention)

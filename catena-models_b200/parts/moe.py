@@ -10,6 +10,13 @@ Routing, the ordering of the (token, choice) pairs by expert and the experts' pr
 device from what the router kernel leaves there, so the part launches the same kernels for every step of
 a shape and its steps can be recorded.  The result is one float32 row per pair; the block's residual sum
 adds a token's rows in the order of its choices.
+
+Further rules of a router, all optional: `correction` (a tensor of one number per router output, added to the scores
+for the choice only; the weights are the scores without it); `groups` and `keep` (the router outputs form `groups` equal
+groups of neighbours, a group's score is its largest choice score, and only members of the best `keep` groups can be
+chosen); `identity` (the last `identity` router outputs stand for experts without matrices whose output is their input
+times the weight; they take part in scores, groups and choice like any other); `scale` (a factor on the weights) and
+`renorm_eps` (added to the sum that `renormalize` divides by).
 """
 from __future__ import annotations
 
@@ -25,16 +32,28 @@ class RoutedSwiGLU(FeedForward):
     supports_append = True
 
     def __init__(self, prefix, hidden, intermediate, experts, top, gate="sigmoid", renormalize=False,
-                 weight_on="input", activation="silu", expert_name="e{}."):
+                 weight_on="input", activation="silu", expert_name="e{}.", correction_name=None, groups=0, keep=0,
+                 identity=0, scale=1.0, renorm_eps=0.0):
         if gate not in ("sigmoid", "softmax") or weight_on not in ("input", "output") or activation not in ("silu", "gelu_tanh"):
             raise ValueError("RoutedSwiGLU: gate sigmoid|softmax, weight_on input|output, activation silu|gelu_tanh")
-        if not 1 <= top <= experts:
+        if top < 1 or experts < 1:
             raise ValueError(f"RoutedSwiGLU: {top} of {experts} experts")
         self.prefix, self.hidden, self.intermediate = prefix, hidden, intermediate
         self.experts, self.top = experts, top
         self.softmax_gate, self.renormalize = gate == "softmax", bool(renormalize)
         self.weight_on_input, self.gelu = weight_on == "input", activation == "gelu_tanh"
         self.expert_name = expert_name
+        self.correction_name, self.groups, self.keep = correction_name, int(groups or 0), int(keep or 0)
+        self.identity, self.scale, self.renorm_eps = int(identity or 0), float(scale), float(renorm_eps)
+        self.outputs = experts + self.identity                 # what the router scores
+        if self.groups and (self.outputs % self.groups or not 1 <= self.keep <= self.groups
+                            or self.keep * (self.outputs // self.groups) < top):
+            raise ValueError(f"RoutedSwiGLU: {self.groups} groups over {self.outputs} router outputs of which {self.keep} stay open, top {top}")
+        if top > self.outputs:
+            raise ValueError(f"RoutedSwiGLU: {top} of {self.outputs} router outputs")
+        if self.identity and self.weight_on_input:
+            raise ValueError("RoutedSwiGLU: identity experts need the weight on the output")
+        self.correction = None
 
     def _names(self, e):
         q = self.prefix + self.expert_name.format(e)
@@ -42,7 +61,9 @@ class RoutedSwiGLU(FeedForward):
 
     def tensor_specs(self):
         H, F = self.hidden, self.intermediate
-        specs = [TensorSpec(self.prefix + "router", (self.experts, H))]
+        specs = [TensorSpec(self.prefix + "router", (self.outputs, H))]
+        if self.correction_name:
+            specs.append(TensorSpec(self.prefix + self.correction_name, (self.outputs,), "vector"))
         for e in range(self.experts):
             g, u, d = self._names(e)
             specs += [TensorSpec(g, (F, H)), TensorSpec(u, (F, H)), TensorSpec(d, (H, F))]
@@ -57,6 +78,8 @@ class RoutedSwiGLU(FeedForward):
         if self.router.dtype != self.w_up.dtype:
             self.router = self.router.to(self.w_up.dtype)
         self._bound = [self.router]
+        if self.correction_name:
+            self.correction = tensors[self.prefix + self.correction_name].to(torch.float32).contiguous()
 
     def weight_bytes(self):
         # a step reads the router and, of the experts, what its tokens choose: at most every expert once
@@ -64,7 +87,7 @@ class RoutedSwiGLU(FeedForward):
         return self.router.numel() * self.router.element_size() + self.experts * per_expert
 
     def forward(self, rt, batch, x):
-        T, top, E = x.shape[0], self.top, self.experts
+        T, top, E = x.shape[0], self.top, self.experts          # E: experts with matrices (they alone get rows)
         P = T * top
         dev = x.device
         if x.dtype != self.w_up.dtype:
@@ -83,7 +106,8 @@ class RoutedSwiGLU(FeedForward):
         work = torch.empty(kernels.moe_work_size(P, E, tile), dtype=torch.int32, device=dev)
         xs = torch.empty((rows, self.hidden), dtype=x.dtype, device=dev) if tensor_cores else None
         kernels.moe_route(ids, wts, perm, dest, work, x, self.router, batch.tok_seq, top, self.softmax_gate, self.renormalize, tile,
-                          xs=xs, apply_weight=self.weight_on_input)
+                          xs=xs, apply_weight=self.weight_on_input, correction=self.correction, groups=self.groups,
+                          keep=self.keep, identity=self.identity, scale=self.scale, renorm_eps=self.renorm_eps)
         a = torch.empty((rows, self.intermediate), dtype=x.dtype, device=dev)
         y = torch.empty((rows, self.hidden), dtype=torch.float32, device=dev)
         if tensor_cores:
@@ -96,7 +120,15 @@ class RoutedSwiGLU(FeedForward):
                                 apply_weight=self.weight_on_input, gelu=self.gelu)
             kernels.moe_grouped(y, a, self.w_down, work, perm, wts, top, max_tiles, up=False,
                                 apply_weight=not self.weight_on_input)
-        return kernels.Terms([(y, 1.0, top, dest)])
+        out = kernels.Terms([(y, 1.0, top, dest)])
+        if self.identity:
+            # the identity experts' share: the input itself, from the float32 stream when the block left it for this
+            src = batch.shared.get("ff_input_f32")
+            src = x if src is None or src.shape != x.shape else src
+            same = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
+            kernels.moe_identity(same, src, ids, wts, top, E)
+            out.append((same, 1.0, 1))
+        return out
 
 
 register_part("feed_forward", "routed_swiglu", RoutedSwiGLU)

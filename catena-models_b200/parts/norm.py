@@ -46,6 +46,18 @@ class RMSNorm(Norm):
         return y
 
 
+class ScalarRMSNorm(RMSNorm):
+    """An RMS norm whose weight is one number for all channels: y = x / sqrt(mean(x^2) + eps) * g.  The number is
+    repeated over the width when it is bound, so every kernel that takes an RMS norm takes this one."""
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (), "norm")]
+
+    def bind(self, tensors, rt):
+        self.weight = tensors[self.name].to(torch.float32).reshape(1).expand(self.width).contiguous()
+        self._bound = [self.weight]
+
+
 class DynamicTanh(Norm):
     """y = tanh(alpha x) * w + b in place of a norm: no mean, no variance, nothing that looks along the row.
     `alpha` is a learned scalar stored as `<name>.alpha`, the shift as `<name>.b`.  Takes float32 rows (a
@@ -78,4 +90,5 @@ class DynamicTanh(Norm):
 
 
 register_part("norm", "rms", RMSNorm)
+register_part("norm", "scalar_rms", ScalarRMSNorm)
 register_part("norm", "dynamic_tanh", DynamicTanh)

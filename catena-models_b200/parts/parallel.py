@@ -10,6 +10,10 @@ norm of whatever runs next are one kernel (`residual_add_norm`), as the sandwich
 `PreNormBlock`: the sequential arrangement on the same stream: a norm and a mixer, then a norm and a
 feed-forward, each sum with a constant factor.
 
+`PostNormBlock`: the norm behind each sum: h <- norm1(c h + mixer(h)), then h <- norm2(c h + feed_forward(h)); the
+sublayers read the stream itself.  Optionally followed by an average over the depth of the stack: what the next layer
+reads is a weighted sum of the embedding output and of every layer's result so far.
+
 `LoopEntry`: the step between two passes of a looped stack: h <- W [h; h0] + step, h0 being the embedding
 rows of the batch (the definition keeps them: `keep_embedding`) and `step` a learned row of the pass.  It
 has no norm of its own and no state; the product's float32 result becomes the new residual stream, and the
@@ -126,6 +130,82 @@ class PreNormBlock(Block):
         return _sum_and_norm(rt, h, self._scaled(self.feed_forward.forward(rt, batch, n2)), None, next_norm)
 
 
+class PostNormBlock(Block):
+    """Two sublayers one after the other on a float32 stream, each followed by a norm over the sum:
+    h <- norm1(c * h + mixer(h)), then h <- norm2(c * h + feed_forward(h)), c = `residual_scale`.  Both sublayers read
+    the stream itself (in the activation dtype); the block has no input norm.  The feed-forward may be absent; its norm
+    then still runs if it is given (over c * h alone).
+
+    `depth_name` (a tensor of `depth_index + 2` numbers) adds an average over the depth: with X_0 the stream before the
+    first block and X_(j+1) the result of block j (before this average), the block leaves sum_j depth[j] * X_j, j = 0 ..
+    depth_index + 1, as the stream.  The X_j of a step are kept in StepBatch.shared["depth_history"] (float32
+    [entries, rows, width]; entry 0 is filled by the model, ModelDefinition.depth_entries says how many there are).
+
+    Each sum, its norm, the average and the rounding of the result for the next reader's products are one kernel
+    (`postnorm_residual`).  A norm is anything with a float32 `weight` row and `eps` (an RMS norm)."""
+    prompt_capturable = True
+    supports_append = True
+
+    def __init__(self, mixer, feed_forward, mixer_norm, ffn_norm, residual_scale=1.0, depth_name=None, depth_index=0):
+        for norm in (mixer_norm, ffn_norm):
+            if norm is not None and getattr(norm, "fused_kind", None) != "rms":
+                raise ValueError("PostNormBlock: its norms are RMS norms")
+        if mixer_norm is None or (feed_forward is not None and ffn_norm is None):
+            raise ValueError("PostNormBlock: every sublayer is followed by a norm")
+        self.mixer, self.feed_forward, self.mixer_norm, self.ffn_norm = mixer, feed_forward, mixer_norm, ffn_norm
+        self.residual_scale = float(residual_scale)
+        self.depth_name, self.depth_index = depth_name, int(depth_index)
+        self.depth = None
+
+    def children(self):
+        return [p for p in (self.mixer, self.mixer_norm, self.feed_forward, self.ffn_norm) if p is not None]
+
+    def tensor_specs(self):
+        return [TensorSpec(self.depth_name, (self.depth_index + 2,), "vector")] if self.depth_name else []
+
+    def bind(self, tensors, rt):
+        if self.depth_name:
+            self.depth = tensors[self.depth_name].to(torch.float32).contiguous()
+            self._bound = [self.depth]
+
+    def state_spec(self):
+        return self.mixer.state_spec()
+
+    def _sum(self, rt, batch, h, terms, norm, last, cast):
+        """h <- norm(c h + terms), then the depth average if this is the block's last sum; the rounded copy if asked."""
+        history = None
+        if last and self.depth is not None:
+            history = batch.shared.get("depth_history")
+            if history is None or history.shape[0] < self.depth_index + 2:
+                raise ValueError("PostNormBlock: the step's depth history is missing or short (ModelDefinition.depth_entries)")
+            history = history[:self.depth_index + 2]
+        n_out = torch.empty(h.shape, dtype=rt.dtype, device=h.device) if cast and rt.dtype != torch.float32 else None
+        kernels.postnorm_residual(h, terms, self.residual_scale, norm.weight, norm.eps, n_out=n_out, history=history,
+                                  coef=self.depth if history is not None else None)
+        if not cast:
+            return None
+        return h if rt.dtype == torch.float32 else n_out
+
+    def forward(self, rt, batch, h, n, state, next_norm):
+        if h.dtype != torch.float32:
+            raise ValueError("PostNormBlock works on a float32 residual stream (ModelDefinition.residual_float32)")
+        batch.partial_sums_ok = False
+        if n is None:
+            n = h if rt.dtype == torch.float32 else h.to(rt.dtype)
+        # the caller forms next_norm itself when there is one (the final norm); else the next block reads the rounded stream
+        cast_last = next_norm is None
+        y = _terms(self.mixer.forward(rt, batch, n, state))
+        if self.ffn_norm is None:
+            return h, self._sum(rt, batch, h, y, self.mixer_norm, True, cast_last)
+        n1 = self._sum(rt, batch, h, y, self.mixer_norm, False, self.feed_forward is not None)
+        f = kernels.Terms()
+        if self.feed_forward is not None:
+            batch.shared["ff_input_f32"] = h            # a feed-forward that hands its input through takes it unrounded
+            f = _terms(self.feed_forward.forward(rt, batch, n1))
+            batch.shared.pop("ff_input_f32", None)
+        return h, self._sum(rt, batch, h, f, self.ffn_norm, True, cast_last)
+
+
 class LoopEntry(Block):
     prompt_capturable = True
     supports_append = True
@@ -155,4 +235,5 @@ class LoopEntry(Block):
 register_part("mixer", "side_by_side", SideBySide)
 register_part("block", "parallel", ParallelBlock)
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "postnorm", PostNormBlock)
 register_part("block", "loop_entry", LoopEntry)

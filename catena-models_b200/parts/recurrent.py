@@ -20,6 +20,9 @@ a running maximum m that starts at 0
 
 then the same unit norm, channel weight, sigmoid(W_g h) gate and output projection.  State: S, n, m, float32.
 
+`GatedDecayMemory` (gated linear attention) and `ConstantDecayMemory` (lightning attention) are described at their
+classes.
+
 Decays, gates, exponentials, the state and every sum over it are float32 whatever the activation dtype;
 the projections run through the runtime's products.  Both mixers run every kind of step through one
 kernel that starts from the stored state (zeros for a new sequence), so a prompt in one step, in portions
@@ -200,6 +203,64 @@ class ConstantDecayMemory(Mixer):
         return self.out.apply(rt, o, out_dtype=self.out_dtype)
 
 
+class GatedDecayMemory(Mixer):
+    """Gated linear attention: q = W_q h / sqrt(dim), k (heads x dim) and v (heads x value_dim); a decay per token, head
+    and key channel out of a low-rank network, w = sigmoid(W_2 (W_1 h) + b)^(1/tau); per head S_t = diag(w_t) S_(t-1) +
+    k_t v_t^T and o_t = S_t^T q_t; each head's o is brought to unit root mean square over its value channels, times a
+    weight per value channel that all heads share, times silu(W_g h), then the output projection.  State per sequence:
+    S, float32, zeros at the start.  The decay (its logits, the logarithm of the sigmoid, the power) is float32."""
+    prompt_capturable = True
+    supports_append = True
+    PRODUCT_RANK = DecayMix.PRODUCT_RANK
+
+    def __init__(self, prefix, hidden, heads, dim, value_dim, rank, tau, eps, out_dtype=None):
+        if not tau > 0:
+            raise ValueError(f"GatedDecayMemory: tau {tau}")
+        self.hidden, self.heads, self.dim, self.value_dim, self.rank = hidden, heads, dim, value_dim, rank
+        self.tau, self.eps, self.prefix = float(tau), float(eps), prefix
+        self.k_size, self.v_size = heads * dim, heads * value_dim
+        self.qkvg = Linear([prefix + "q", prefix + "k", prefix + "v", prefix + "g"],
+                           [self.k_size, self.k_size, self.v_size, self.v_size], hidden)
+        self.out = Linear(prefix + "o", hidden, self.v_size)
+        self.out_dtype = {None: None, "float32": torch.float32}[out_dtype]
+
+    def children(self):
+        return [self.qkvg, self.out]
+
+    def tensor_specs(self):
+        p = self.prefix
+        return [TensorSpec(p + "a1", (self.rank, self.hidden)), TensorSpec(p + "a2", (self.k_size, self.rank)),
+                TensorSpec(p + "a2.b", (self.k_size,), "vector"), TensorSpec(p + "norm", (self.value_dim,), "vector")]
+
+    def bind(self, tensors, rt):
+        p = self.prefix
+        self.a1 = tensors[p + "a1"].contiguous()
+        self.a2_rows = tensors[p + "a2"].contiguous()              # as stored, for the products
+        self.a2 = tensors[p + "a2"].t().contiguous()               # [rank, channels], for the one-kernel form
+        self.bias = tensors[p + "a2.b"].to(torch.float32).contiguous()
+        self.norm_w = tensors[p + "norm"].to(torch.float32).repeat(self.heads).contiguous()     # the scan indexes head x channel
+        self._bound = [self.a1, self.a2, self.bias, self.norm_w]
+
+    def state_spec(self):
+        return FixedStateSpec((self.heads * self.dim * self.value_dim,), "float32")
+
+    def forward(self, rt, batch, x, state):
+        T, KS, VS = batch.T, self.k_size, self.v_size
+        proj = self.qkvg.apply(rt, x)
+        decay = torch.empty((T, KS), dtype=torch.float32, device=x.device)
+        if self.rank >= self.PRODUCT_RANK and self.rank % 8 == 0 and self.hidden % 8 == 0:
+            low = rt.linear(x, self.a1)
+            kernels.decay_from_logits(decay, rt.linear(low, self.a2_rows, out_dtype=torch.float32), self.bias, tau=self.tau)
+        else:
+            kernels.lowrank_decay(decay, x, self.a1, self.a2, self.bias, tau=self.tau)
+        o = torch.empty((T, VS), dtype=x.dtype, device=x.device)
+        kernels.matrix_scan("gated", o, proj[:, :KS], proj[:, KS:2 * KS], proj[:, 2 * KS:2 * KS + VS],
+                            proj[:, 2 * KS + VS:], decay, None, self.norm_w, state.tensor, 0, batch.seq_start,
+                            batch.seq_slot, batch.B, self.heads, self.dim, self.value_dim, self.dim ** -0.5, self.eps)
+        return self.out.apply(rt, o, out_dtype=self.out_dtype)
+
+
 register_part("mixer", "decay_mix", DecayMix)
+register_part("mixer", "gated_decay_memory", GatedDecayMemory)
 register_part("mixer", "constant_decay_memory", ConstantDecayMemory)
 register_part("mixer", "matrix_memory", MatrixMemory)

@@ -77,6 +77,28 @@ class PartialYarnRotary(Position):
         return self._rate
 
 
+class PairedRotary(Position):
+    """Rotation of the leading `dims` channels of a vector, channel 2i against channel 2i + 1 (the interleaved layout),
+    pair i at the rate theta^(-2i/dims); the other channels pass unchanged.  The rates are formed in double precision on
+    the host and kept as float32; the kernel forms angle = float(position) * rate."""
+    prompt_capturable = True
+    supports_append = True
+    pairing = "interleaved"
+
+    def __init__(self, dims, theta):
+        if dims % 2 or dims < 2:
+            raise ValueError(f"{dims} turned channels: an even number is needed")
+        self.dims, self.theta = dims, float(theta)
+        self.rates = [self.theta ** (-2.0 * i / dims) for i in range(dims // 2)]
+        self._rate = None
+
+    def bind(self, tensors, rt):
+        self._rate = torch.tensor(self.rates, dtype=torch.float64).to(torch.float32).to(rt.device).contiguous()
+
+    def rate_table(self):
+        return self._rate
+
+
 class NoPosition(Position):
     """No position encoding: the head vectors are left unrotated."""
     prompt_capturable = True
@@ -86,4 +108,5 @@ class NoPosition(Position):
 
 register_part("position", "rotary", Rotary)
 register_part("position", "none", NoPosition)
+register_part("position", "paired_rotary", PairedRotary)
 register_part("position", "partial_yarn_rotary", PartialYarnRotary)
