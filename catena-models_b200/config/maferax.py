@@ -60,6 +60,7 @@ class LayerConfig:
     type: str                # gla | latent_attention
     mixer: object
     mlp: object              # MlpConfig or None
+    norm_alone: bool = False # no feed-forward, but the layer's second norm runs all the same (its tensor is there)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -160,9 +161,12 @@ class MaferaxConfig:
             raise ConfigError(f"{where}: " + "; ".join(problems))
 
     def with_tensor_shapes(self, shapes):
-        """The same configuration with the sizes that only the tensors give (the decay network's rank)."""
+        """The same configuration with what only the tensors give: the decay network's rank, and whether a layer without
+        a feed-forward has a second norm (`l<i>.norm2`)."""
         layers = []
         for i, layer in enumerate(self.layers):
+            if layer.mlp is None and f"l{i}.norm2" in shapes:
+                layer = dataclasses.replace(layer, norm_alone=True)
             if layer.type == "gla" and layer.mixer.rank == 0:
                 shape = shapes.get(f"l{i}.mix.a1")
                 if shape is None or len(shape) != 2:

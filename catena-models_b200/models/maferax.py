@@ -56,7 +56,7 @@ def define(cfg: MaferaxConfig) -> ModelDefinition:
     for i, layer in enumerate(cfg.layers):
         ff = _feed_forward(cfg, i, layer.mlp)
         blocks.append(build_part("block", "postnorm", mixer=_mixer(cfg, i, layer), feed_forward=ff,
-                                 mixer_norm=norm(f"l{i}.norm1"), ffn_norm=norm(f"l{i}.norm2") if ff is not None else None,
+                                 mixer_norm=norm(f"l{i}.norm1"), ffn_norm=norm(f"l{i}.norm2") if ff is not None or layer.norm_alone else None,
                                  residual_scale=cfg.postln_alpha, depth_name=f"l{i}.dwa", depth_index=i))
         plan.append(PlanEntry(block=i, state=i))
     return ModelDefinition(architecture=cfg.architecture, vocab_size=cfg.vocab, hidden_size=W, embedding_name="embed",

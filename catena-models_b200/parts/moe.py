@@ -94,7 +94,7 @@ class RoutedSwiGLU(FeedForward):
             raise ValueError("RoutedSwiGLU: activations and expert matrices must share a dtype")
         # bfloat16 with rows that TMA can fetch: the grouped tcgen05 product over row tiles of 128; else the CUDA cores
         tensor_cores = (x.dtype == torch.bfloat16 and not self.gelu and self.hidden % 8 == 0 and self.intermediate % 8 == 0
-                        and self.weight_on_input and (rt.tensor_core_prompts or batch.kind == "decode")
+                        and (rt.tensor_core_prompts or batch.kind == "decode")
                         and rt.grouped_tensor_cores)
         tile = kernels.MOE_TILE_TC if tensor_cores else kernels.MOE_TILE_SIMT
         max_tiles = kernels.moe_max_tiles(P, E, tile)
@@ -120,7 +120,8 @@ class RoutedSwiGLU(FeedForward):
                                 apply_weight=self.weight_on_input, gelu=self.gelu)
             kernels.moe_grouped(y, a, self.w_down, work, perm, wts, top, max_tiles, up=False,
                                 apply_weight=not self.weight_on_input)
-        out = kernels.Terms([(y, 1.0, top, dest)])
+        # the grouped tensor-core product has no weights of its own: on the outputs they ride on the residual sum's pieces
+        out = kernels.Terms([(y, 1.0, top, dest, wts) if tensor_cores and not self.weight_on_input else (y, 1.0, top, dest)])
         if self.identity:
             # the identity experts' share: the input itself, from the float32 stream when the block left it for this
             src = batch.shared.get("ff_input_f32")
