@@ -559,6 +559,26 @@ def fozedra_config(size, vocab=VOCAB):
     return dict(architecture="Fozedra", vocab=vocab, width=z["width"], norm=dict(eps=1e-6), residual_mult=0.6, layers=layers)
 
 
+def maferax_config(size, vocab=VOCAB):
+    """For `--compare maferax`: eight layers of the Maferax decoder at the same width, heads and feed-forward widths as the
+    Narasun model above: four layers of gated linear attention (the matrix memory's head sizes, a decay network of the decay
+    mix's rank) and four of latent attention (the attention's heads; a latent of a quarter of the width plus a turned part of
+    32 channels per token instead of keys and values per head), dense and routed feed-forwards in turn; the router has
+    four identity experts beside the real ones, three groups of which two stay open."""
+    z = COMPARE_SIZES[size]
+    lin = lambda mlp: dict(type="gla", mlp=mlp, mixer=dict(heads=z["mem_heads"], dim=z["mem_dim"], vdim=z["mem_vdim"], tau=16.0,
+                                                           rank=z["rank"]))
+    lat = lambda mlp: dict(type="latent_attention", mlp=mlp, mixer=dict(
+        heads=z["heads"], dim=z["head"], rot_dim=32, vdim=z["head"], kv_rank=z["width"] // 4, q_rank=3 * z["width"] // 8,
+        scale=(z["head"] + 32) ** -0.5, rot=dict(dims=32, base=1000000.0)))
+    dense = dict(kind="dense", ff=z["ff"])
+    moe = dict(kind="moe", expert=dict(ff=z["expert_ff"]),
+               router=dict(experts=z["experts"], top=z["top"], identity=4, scale=2.0, groups=dict(count=3, keep=2)))
+    layers = [lin(dense), lat(moe), lin(moe), lat(dense), lin(dense), lat(moe), lin(moe), lat(dense)]
+    return dict(architecture="Maferax", vocab=vocab, width=z["width"], norm=dict(eps=1e-6), postln_alpha=3.0, logit_scale=0.25,
+                layers=layers)
+
+
 def lfm3_like_config(size, vocab=VOCAB):
     z = COMPARE_SIZES[size]
     return dict(architecture="lfm3", vocab_size=vocab, hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=8,
@@ -638,7 +658,7 @@ def _kernel_rows(torch, model, prompt_len, batch, vocab):
 
 def compare_designs(which, sizes, prompt_len, batch, steps, pk, tables):
     """Prefill and decode throughput of a design beside the closest earlier one at equal size, random weights: the
-    Narasun decoder beside an LFM3 decoder, the Fozedra decoder beside the Narasun decoder."""
+    Narasun decoder beside an LFM3 decoder, the Fozedra and the Maferax decoder beside the Narasun decoder."""
     import torch
 
     from catena_models_b200.api import Model
@@ -651,7 +671,8 @@ def compare_designs(which, sizes, prompt_len, batch, steps, pk, tables):
     print("|---|---|---|---|---|---|---|---|---|---|")
     for size in sizes:
         pairs = {"narasun": (("Narasun", narasun_config), ("LFM3", lfm3_like_config)),
-                 "fozedra": (("Fozedra", fozedra_config), ("Narasun", narasun_config))}[which]
+                 "fozedra": (("Fozedra", fozedra_config), ("Narasun", narasun_config)),
+                 "maferax": (("Maferax", maferax_config), ("Narasun", narasun_config))}[which]
         for name, cfg in ((n, make(size, vocab)) for n, make in pairs):
             model = Model.random(cfg, seed=0, std=0.02, dtype="bfloat16", max_tokens=batch * (prompt_len + 256) + 4096,
                                  max_seqs=batch + 1)
@@ -691,9 +712,9 @@ def main():
                     help="time one decode step and one prompt step kernel by kernel and print the table")
     ap.add_argument("--attention-table", action="store_true",
                     help="time the prompt-attention kernels alone at 2,048, 4,096 and 16,384 tokens and print the table")
-    ap.add_argument("--compare", default=None, choices=["narasun", "fozedra"],
+    ap.add_argument("--compare", default=None, choices=["narasun", "fozedra", "maferax"],
                     help="instead of the JSON line: prompt and decode throughput of that design beside the closest earlier "
-                         "one at equal size (random weights: Narasun beside LFM3, Fozedra beside Narasun), as a table")
+                         "one at equal size (random weights: Narasun beside LFM3, Fozedra and Maferax beside Narasun), as a table")
     ap.add_argument("--compare-sizes", default="1024,2048", help="widths of `--compare`")
     ap.add_argument("--compare-kernels", action="store_true", help="with `--compare`: also each model's kernel tables")
     ap.add_argument("--print-config", action="store_true",

@@ -28,7 +28,12 @@ latent_prepare_kernel(const LatentArgs a) {
     pdl_wait();
     const long long t = blockIdx.x;
     const int b = a.tok_seq[t];
-    if (b < 0) return;
+    T* copy = a.ckv ? (T*)a.ckv + t * a.EC : nullptr;
+    if (b < 0) {
+        if (copy)
+            for (int c = threadIdx.x; c < a.EC; c += blockDim.x) copy[c] = from_f32<T>(0.f);
+        return;
+    }
     const T* row = (const T*)a.proj + t * a.ld_proj;
     // the query latent
     {
@@ -69,6 +74,97 @@ latent_prepare_kernel(const LatentArgs a) {
         entry[a.KR + 2 * i + 1] = from_f32<T>(v * cs + u * sn);
     }
     for (int c = a.KR + a.R + threadIdx.x; c < a.EC; c += blockDim.x) entry[c] = from_f32<T>(0.f);
+    if (copy) {
+        __syncthreads();                               // the entry is complete (every thread reads what others wrote)
+        for (int c = threadIdx.x; c < a.EC; c += blockDim.x) copy[c] = entry[c];
+    }
+}
+
+// The prompt form's operands: per row, queries, keys and values of every head in heads of HD channels, as the attention
+// kernels over keys and values take them: q = [q_plain | q_turn turned | 0], k = [W_uk c | the row's turned key part | 0],
+// v = [W_uv c | 0].  One block per row; the row's angles are formed once and serve every head.  VEC: eight channels per
+// access (every size a multiple of 8, rows and buffers aligned to match).
+#define LX_MAX_PAIRS 256
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+latent_expand_kernel(const LatentArgs a) {
+    __shared__ float cs_tab[LX_MAX_PAIRS], sn_tab[LX_MAX_PAIRS];
+    pdl_trigger();
+    pdl_wait();
+    const long long t = blockIdx.x;
+    const int H = a.H, D = a.D, R = a.R, DV = a.DV, HD = a.HD;
+    T* out = (T*)a.qkv + t * a.ld_qkv;
+    const bool pad = a.tok_seq[t] < 0;
+    const T* q = (const T*)a.q + t * a.ldq;
+    const T* kvu = (const T*)a.kvu + t * a.ld_kvu;
+    const T* r = (const T*)a.ckv + t * a.EC + a.KR;
+    const float pos = pad ? 0.f : (float)a.tok_pos[t];
+    for (int i = threadIdx.x; i < R / 2; i += blockDim.x) sincosf(pos * a.rate[i], &sn_tab[i], &cs_tab[i]);
+    __syncthreads();
+    const int n = H * HD;
+    if (VEC) {
+        const int n8 = n >> 3;
+        for (int e8 = threadIdx.x; e8 < 3 * n8; e8 += blockDim.x) {
+            const int which = e8 / n8, hc = (e8 - which * n8) * 8, h = hc / HD, c = hc - h * HD;
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (!pad) {
+                if (which == 0) {
+                    if (c < D + R) load8f<T>(q + h * (D + R) + c, v);
+                    if (c >= D && c < D + R) {
+                        const int i0 = (c - D) >> 1;
+#pragma unroll
+                        for (int p = 0; p < 4; ++p) {
+                            const float cs = cs_tab[i0 + p], sn = sn_tab[i0 + p], u = v[2 * p], w = v[2 * p + 1];
+                            v[2 * p] = u * cs - w * sn;
+                            v[2 * p + 1] = w * cs + u * sn;
+                        }
+                    }
+                } else if (which == 1) {
+                    if (c < D) load8f<T>(kvu + h * D + c, v);
+                    else if (c < D + R) load8f<T>(r + (c - D), v);
+                } else if (c < DV) load8f<T>(kvu + H * D + h * DV + c, v);
+            }
+            store8f<T>(out + (long long)e8 * 8, v);
+        }
+        return;
+    }
+    for (int e = threadIdx.x; e < 3 * n; e += blockDim.x) {
+        const int which = e / n, hc = e - which * n, h = hc / HD, c = hc - h * HD;
+        float v = 0.f;
+        if (!pad) {
+            if (which == 0) {
+                if (c < D) v = to_f32(q[h * (D + R) + c]);
+                else if (c < D + R) {
+                    const int i = (c - D) >> 1;
+                    const T* pair = q + h * (D + R) + D + 2 * i;
+                    if (2 * i + 1 >= R) v = to_f32(pair[0]);          // an odd last channel has no partner
+                    else {
+                        const float u = to_f32(pair[0]), w = to_f32(pair[1]);
+                        v = ((c - D) & 1) ? w * cs_tab[i] + u * sn_tab[i] : u * cs_tab[i] - w * sn_tab[i];
+                    }
+                }
+            } else if (which == 1) {
+                if (c < D) v = to_f32(kvu[h * D + c]);
+                else if (c < D + R) v = to_f32(r[c - D]);
+            } else if (c < DV) v = to_f32(kvu[H * D + h * DV + c]);
+        }
+        out[e] = from_f32<T>(v);
+    }
+}
+
+extern "C" int cm_latent_expand(int dt, const LatentArgs* args, cudaStream_t st) {
+    const LatentArgs& a = *args;
+    if (a.rows <= 0) return CM_OK;
+    if (a.HD < a.D + a.R || a.HD < a.DV || !a.ckv || !a.kvu || !a.qkv || !a.q || a.R / 2 > LX_MAX_PAIRS)
+        CM_REFUSE("latent_expand: heads of %d channels for %d + %d and %d", a.HD, a.D, a.R, a.DV);
+    const bool vec = ((a.D | a.R | a.DV | a.HD | a.KR | a.EC) % 8 == 0) && ((a.ldq | a.ld_kvu | a.ld_qkv) % 8 == 0) &&
+                     (((uintptr_t)a.q | (uintptr_t)a.kvu | (uintptr_t)a.ckv | (uintptr_t)a.qkv) & 15) == 0 && dt == DT_BF16;
+    if (dt == DT_F32) cm_launch(latent_expand_kernel<float, false>, (unsigned)a.rows, 256, 0, st, a);
+    else if (dt == DT_BF16 && vec) cm_launch(latent_expand_kernel<bf16, true>, (unsigned)a.rows, 256, 0, st, a);
+    else if (dt == DT_BF16) cm_launch(latent_expand_kernel<bf16, false>, (unsigned)a.rows, 256, 0, st, a);
+    else return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
 }
 
 // The turned part of every head's query, moved behind the place of the query against the latent:
@@ -182,14 +278,50 @@ head_linear_kernel(TY* __restrict__ y, const TX* __restrict__ x, const T* __rest
     }
 }
 
+// The same for a few rows (single-token steps): the tiles above would be nearly empty.  A warp owns one output column of
+// one head: its lanes walk the matrix row once and meet up to HL_FEW rows of x with it; sums over lanes by shuffles.
+#define HL_FEW 8
+template <typename TX, typename T, typename TY>
+__global__ void __launch_bounds__(256)
+head_linear_few_kernel(TY* __restrict__ y, const TX* __restrict__ x, const T* __restrict__ w, long long rows, int N, int K,
+                       long long ldx, long long ldy, int xs, int ys) {
+    pdl_trigger();
+    pdl_wait();
+    const int h = blockIdx.y, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (n >= N) return;
+    const T* wr = w + ((long long)h * N + n) * K;
+    const TX* xh = x + (long long)h * xs;
+    for (long long r0 = 0; r0 < rows; r0 += HL_FEW) {
+        float acc[HL_FEW];
+#pragma unroll
+        for (int r = 0; r < HL_FEW; ++r) acc[r] = 0.f;
+        for (int k = lane; k < K; k += 32) {
+            const float wv = to_f32(wr[k]);
+#pragma unroll
+            for (int r = 0; r < HL_FEW; ++r)
+                if (r0 + r < rows) acc[r] = fmaf(to_f32(xh[(r0 + r) * ldx + k]), wv, acc[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < HL_FEW; ++r) {
+            const float v = warp_sum(acc[r]);
+            if (lane == 0 && r0 + r < rows) y[(r0 + r) * ldy + (long long)h * ys + n] = from_f32<TY>(v);
+        }
+    }
+}
+
 // x_f32 / y_f32: the rows read / written are float whatever the matrices' dtype (sums that stay unrounded between two steps).
 extern "C" int cm_head_linear(int dt, void* y, const void* x, const void* w, long long rows, int H, int N, int K, long long ldx,
                               long long ldy, int xs, int ys, int x_f32, int y_f32, cudaStream_t st) {
     if (rows <= 0 || H <= 0 || N <= 0) return CM_OK;
     if (H > 65535) CM_REFUSE("head_linear: %d heads", H);
-    dim3 grid((N + HL_TN - 1) / HL_TN, (unsigned)((rows + HL_TM - 1) / HL_TM), H);
+    const bool few = rows <= 2 * HL_FEW;
+    dim3 grid(few ? (N + 7) / 8 : (N + HL_TN - 1) / HL_TN, few ? H : (unsigned)((rows + HL_TM - 1) / HL_TM), few ? 1 : H);
 #define HL_LAUNCH(TX, TW, TY) \
-    cm_launch(head_linear_kernel<TX, TW, TY>, grid, 256, 0, st, (TY*)y, (const TX*)x, (const TW*)w, rows, N, K, ldx, ldy, xs, ys)
+    do {                                                                                                                    \
+        if (few) cm_launch(head_linear_few_kernel<TX, TW, TY>, grid, 256, 0, st, (TY*)y, (const TX*)x, (const TW*)w, rows, N, K, ldx, ldy, xs, ys); \
+        else cm_launch(head_linear_kernel<TX, TW, TY>, grid, 256, 0, st, (TY*)y, (const TX*)x, (const TW*)w, rows, N, K, ldx, ldy, xs, ys);         \
+    } while (0)
     if (dt == DT_F32) HL_LAUNCH(float, float, float);
     else if (dt == DT_BF16 && x_f32 && y_f32) HL_LAUNCH(float, bf16, float);
     else if (dt == DT_BF16 && x_f32) HL_LAUNCH(float, bf16, bf16);
@@ -242,6 +374,7 @@ latent_attn_kernel(const LatentArgs a) {
         const int r = r0 + warp * 4 + m;
         row_pos[m] = r < n_rows ? pos0 + r / H : -1;
     }
+    const bool warp_live = r0 + warp * 4 < n_rows;    // a warp without rows (fewer heads than the block has rows) only fetches
     const int last_row = min(n_rows, r0 + LA_ROWS) - 1;
     const int k_first = a.splits > 1 ? split * a.chunk : 0;
     const int k_last = min(pos0 + last_row / H, a.splits > 1 ? k_first + a.chunk - 1 : 0x7fffffff);     // inclusive
@@ -273,6 +406,7 @@ latent_attn_kernel(const LatentArgs a) {
             }
         }
         __syncthreads();
+        if (!warp_live) continue;                     // warp-uniform: the block's barriers stand at the loop's head
         // scores of key k0 + lane against the warp's four rows
         float s[4] = {0.f, 0.f, 0.f, 0.f};
         const float* kr = sk + lane * EK;
@@ -349,42 +483,68 @@ latent_attn_kernel(const LatentArgs a) {
     }
 }
 
-// The splits of a row merged in their order, normalised and gated.  One warp per (row, head).
+// The splits of a row merged in their order, normalised and gated.  One block per (row, head): the splits' weights
+// exp(maximum - the row's maximum) are formed once, then every thread adds up its channels over the splits, with loads
+// that do not wait for one another.
+#define LA_MAX_SPLITS 1024
+#define LA_MERGE_THREADS 128
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(LA_MERGE_THREADS)
 latent_attn_merge_kernel(const LatentArgs a) {
+    __shared__ float ws[LA_MAX_SPLITS];
+    __shared__ float red[LA_MERGE_THREADS / 32];
     pdl_trigger();
     pdl_wait();
-    const long long idx = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (idx >= a.rows * a.H) return;
+    const long long idx = blockIdx.x;
     const long long t = idx / a.H;
-    const int h = (int)(idx - t * a.H), lane = threadIdx.x & 31, KR = a.KR;
+    const int h = (int)(idx - t * a.H), KR = a.KR, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (a.tok_seq[t] < 0) return;
-    const float* part = a.parts + idx * a.splits * (2 + KR);
+    const long long stride = 2 + KR;
+    const float* part = a.parts + idx * a.splits * stride;
     float mx = -INFINITY;
-    for (int s = 0; s < a.splits; ++s) mx = fmaxf(mx, part[(long long)s * (2 + KR)]);
+    for (int s = tid; s < a.splits; s += LA_MERGE_THREADS) mx = fmaxf(mx, part[s * stride]);
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = red[0];
+#pragma unroll
+    for (int w = 1; w < LA_MERGE_THREADS / 32; ++w) mx = fmaxf(mx, red[w]);
+    __syncthreads();
+    for (int s = tid; s < a.splits; s += LA_MERGE_THREADS) {
+        const float m = part[s * stride];
+        ws[s] = m == -INFINITY ? 0.f : expf(m - mx);
+    }
+    __syncthreads();
+    // the sum in the splits' order, by every thread for itself: no exchange, and the same digits in every thread
     float sum = 0.f;
-    for (int s = 0; s < a.splits; ++s) {
-        const float m = part[(long long)s * (2 + KR)];
-        if (m != -INFINITY) sum = fmaf(part[(long long)s * (2 + KR) + 1], expf(m - mx), sum);
-    }
+    for (int s = 0; s < a.splits; ++s) sum = fmaf(part[s * stride + 1], ws[s], sum);
     const float g = a.gate ? sigmoid_f32(to_f32(((const T*)a.gate)[t * a.ld_gate + h])) : 1.f;
+    const float f = g / sum;
     float* o = a.out + t * a.ldo + (long long)h * KR;
-    for (int c = lane; c < KR; c += 32) {
+    for (int c = tid; c < KR; c += LA_MERGE_THREADS) {
         float v = 0.f;
-        for (int s = 0; s < a.splits; ++s) {
-            const float m = part[(long long)s * (2 + KR)];
-            if (m != -INFINITY) v = fmaf(part[(long long)s * (2 + KR) + 2 + c], expf(m - mx), v);
-        }
-        o[c] = v * (g / sum);
+#pragma unroll 8
+        for (int s = 0; s < a.splits; ++s) v = fmaf(part[s * stride + 2 + c], ws[s], v);
+        o[c] = v * f;
     }
+}
+
+int cm_latent_attn_merge(int dt, const LatentArgs* args, cudaStream_t st) {
+    const LatentArgs& a = *args;
+    if (a.splits > LA_MAX_SPLITS) CM_REFUSE("latent_attn: %d splits", a.splits);
+    const unsigned mgrid = (unsigned)(a.rows * a.H);
+    if (dt == DT_F32) cm_launch(latent_attn_merge_kernel<float>, mgrid, LA_MERGE_THREADS, 0, st, a);
+    else if (dt == DT_BF16) cm_launch(latent_attn_merge_kernel<bf16>, mgrid, LA_MERGE_THREADS, 0, st, a);
+    else return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
 }
 
 extern "C" int cm_latent_attn(int dt, const LatentArgs* args, cudaStream_t st) {
     const LatentArgs& a = *args;
     if (a.rows <= 0 || a.B <= 0 || a.max_len <= 0) return CM_OK;
     if (a.E != a.KR + a.R || a.KR < 1 || a.KR > 512) CM_REFUSE("latent_attn: latents of %d channels (up to 512)", a.KR);
-    if (a.splits < 1 || (a.splits > 1 && (!a.parts || a.chunk < LA_KT || a.chunk % LA_KT)))
+    if (a.splits < 1 || a.splits > LA_MAX_SPLITS || (a.splits > 1 && (!a.parts || a.chunk < LA_KT || a.chunk % LA_KT)))
         CM_REFUSE("latent_attn: %d splits of %d keys", a.splits, a.chunk);
     const int EQ = (a.E + 3) & ~3, EK = a.E | 1;
     const size_t smem = (size_t)(LA_ROWS * EQ + LA_KT * EK) * sizeof(float);
@@ -405,11 +565,6 @@ extern "C" int cm_latent_attn(int dt, const LatentArgs* args, cudaStream_t st) {
         return CM_ERR_DTYPE;
 #undef LA_LAUNCH
     CM_CHECK_LAUNCH();
-    if (a.splits > 1) {
-        const unsigned mgrid = (unsigned)((a.rows * a.H + 3) / 4);
-        if (dt == DT_F32) cm_launch(latent_attn_merge_kernel<float>, mgrid, 128, 0, st, a);
-        else cm_launch(latent_attn_merge_kernel<bf16>, mgrid, 128, 0, st, a);
-        CM_CHECK_LAUNCH();
-    }
+    if (a.splits > 1) return cm_latent_attn_merge(dt, args, st);
     return CM_OK;
 }

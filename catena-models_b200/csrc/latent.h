@@ -31,4 +31,15 @@ struct LatentArgs {
     int B, max_len;              // sequences; the longest run of new rows (the grid's bound)
     int splits, chunk;           // keys [s * chunk, (s + 1) * chunk) belong to split s; splits == 1: one block walks them all
     float* parts;                // splits > 1: [rows * H][splits][2 + KR] (maximum, sum, unnormalised output)
+    // the prompt form that expands the latents into keys and values per head
+    void* ckv;                   // [rows][EC] (or null): the step's cache entries once more, side by side, for a product
+    const void* kvu;             // [rows][ld_kvu]: per head the unturned key (H * D), then per head the value (H * DV)
+    long long ld_kvu;
+    void* qkv;                   // [rows][ld_qkv]: queries, keys and values in heads of HD channels, zeros behind each head
+    long long ld_qkv;
+    int HD, DV;
 };
+
+// The splits' (maximum, sum, sums over the latents) of every (row, head) merged, normalised and gated (latent.cu); both
+// forms of the attention end with it.
+int cm_latent_attn_merge(int dt, const LatentArgs* args, cudaStream_t st);

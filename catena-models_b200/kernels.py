@@ -72,7 +72,9 @@ _SIGNATURES = {
     "cm_moe_identity": [_i, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
     "cm_latent_prepare": [_i, _vp, _vp],
     "cm_latent_query_turn": [_i, _vp, _vp],
+    "cm_latent_expand": [_i, _vp, _vp],
     "cm_latent_attn": [_i, _vp, _vp],
+    "cm_latent_attn_mma": [_vp, _vp],
     "cm_head_linear": [_i, _vp, _vp, _vp, _ll, _i, _i, _i, _ll, _ll, _i, _i, _i, _i, _vp],
     "cm_moe_gather": [_i, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
     "cm_gemm_tc_grouped": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _i, _vp, _vp],
@@ -1074,7 +1076,16 @@ class _LatentArgs(ctypes.Structure):
                 ("out", _vp), ("ldo", _ll), ("H", _i), ("D", _i), ("R", _i), ("KR", _i), ("QR", _i), ("E", _i), ("EC", _i),
                 ("eps", _f), ("scale", _f), ("rows", _ll), ("tok_pos", _vp), ("tok_seq", _vp), ("seq_start", _vp),
                 ("seq_pos0", _vp), ("seq_end", _vp), ("seq_slot", _vp), ("pool", _vp), ("ptab", _vp), ("ptab_stride", _ll),
-                ("B", _i), ("max_len", _i), ("splits", _i), ("chunk", _i), ("parts", _vp)]
+                ("B", _i), ("max_len", _i), ("splits", _i), ("chunk", _i), ("parts", _vp), ("ckv", _vp), ("kvu", _vp),
+                ("ld_kvu", _ll), ("qkv", _vp), ("ld_qkv", _ll), ("HD", _i), ("DV", _i)]
+
+
+latent_decode_tensor_cores = True   # off: single-token steps of the latent attention stay on the CUDA cores (tests compare)
+
+
+def set_latent_decode_tensor_cores(on):
+    global latent_decode_tensor_cores
+    latent_decode_tensor_cores = bool(on)
 
 
 LATENT_KEY_TILE = 32               # csrc/latent.cu: cache entries of a key tile; a split's keys are a multiple of it
@@ -1093,15 +1104,19 @@ def _latent_args(batch, pool, ptab, H, D, R, KR, QR, eps=0.0, scale=1.0, **field
                        splits=1, chunk=0, **fields)
 
 
-def latent_prepare(cq, proj, q_off, kv_off, wq_norm, wkv_norm, rate, pool, ptab, batch, H, D, R, KR, QR, eps):
+def latent_prepare(cq, proj, q_off, kv_off, wq_norm, wkv_norm, rate, pool, ptab, batch, H, D, R, KR, QR, eps, entries=None):
     """Per row of the step: cq = norm(proj[q_off : q_off + QR]) * wq_norm (activation dtype, for the product that
     makes the heads' queries), and the row's cache entry [norm(proj[kv_off : kv_off + KR]) * wkv_norm | the next R
     channels turned by the position (pairs 2i, 2i + 1 by position * rate[i]) | zeros] into pool [pages, PAGE_TOKENS, EC]
-    through the page table.  Norms and angles are float32."""
+    through the page table.  Norms and angles are float32.  `entries` [rows, EC] (contiguous): the same entries once
+    more in the order of the step's rows (zeros for rows of padding), for a product over them."""
     a = _latent_args(batch, pool, ptab, H, D, R, KR, QR, eps=eps, proj=_ptr(proj), ld_proj=proj.stride(0), q_off=q_off,
-                     kv_off=kv_off, cq=_ptr(cq), wq_norm=_ptr(wq_norm), wkv_norm=_ptr(wkv_norm), rate=_ptr(rate))
+                     kv_off=kv_off, cq=_ptr(cq), wq_norm=_ptr(wq_norm), wkv_norm=_ptr(wkv_norm), rate=_ptr(rate),
+                     ckv=_ptr(entries))
     if proj.stride(1) != 1 or not cq.is_contiguous() or cq.dtype != proj.dtype or pool.dtype != proj.dtype:
         raise KernelError("latent_prepare: row-major operands of one dtype")
+    if entries is not None and (entries.shape != (batch.T, pool.shape[-1]) or not entries.is_contiguous() or entries.dtype != pool.dtype):
+        raise KernelError("latent_prepare: the entries' copy is [rows, entry size] in the cache's dtype")
     _check(lib().cm_latent_prepare(dtype_code(proj.dtype), ctypes.byref(a), _stream()), "latent_prepare",
            cost=lambda: (f"{batch.T} rows, {QR} + {KR} + {R}", batch.T * (2 * QR + 2 * (KR + R)) * proj.element_size(), 6 * batch.T * (QR + KR)))
 
@@ -1115,22 +1130,41 @@ def latent_query_turn(qa, q, rate, pool, ptab, batch, H, D, R, KR):
            cost=lambda: (f"{batch.T} rows, {H} heads of {R}", batch.T * H * R * (4 + q.element_size()), 6 * batch.T * H * R))
 
 
-def latent_attn_splits(rows, H, keys, sm_count=148):
-    """(splits, keys per split) for a step of `rows` single-token rows over up to `keys` cache entries: enough blocks
-    to fill the device, a split at least four key tiles long."""
-    blocks = -(-rows * H // 32)
+def latent_expand(qkv, q, kvu, entries, rate, pool, ptab, batch, H, D, R, DV, KR, HD):
+    """The operands of an attention over keys and values per head, for a prompt step: qkv [rows, 3 * H * HD] =
+    per head [q_plain | q_turn turned by the position | 0], then per head [kvu's unturned key | the row's turned key
+    part from `entries` | 0], then per head [kvu's value | 0].  q [rows, H * (D + R)] as the product left it; kvu
+    [rows, H * D + H * DV] = [W_uk; W_uv] times the row's latent; entries [rows, EC] from `latent_prepare`.  Rows of
+    padding become zeros."""
+    a = _latent_args(batch, pool, ptab, H, D, R, KR, 0, q=_ptr(q), ldq=q.stride(0), rate=_ptr(rate), ckv=_ptr(entries),
+                     kvu=_ptr(kvu), ld_kvu=kvu.stride(0), qkv=_ptr(qkv), ld_qkv=qkv.stride(0), HD=HD, DV=DV)
+    if (qkv.shape[1] != 3 * H * HD or kvu.shape[1] != H * (D + DV) or q.shape[1] != H * (D + R) or not entries.is_contiguous()
+            or any(t.stride(1) != 1 or t.dtype != qkv.dtype for t in (qkv, q, kvu, entries))):
+        raise KernelError("latent_expand: row-major operands of one dtype, heads of HD channels")
+    _check(lib().cm_latent_expand(dtype_code(qkv.dtype), ctypes.byref(a), _stream()), "latent_expand",
+           cost=lambda: (f"{batch.T} rows, {H} heads of {D}+{R} and {DV} in {HD}",
+                         batch.T * (3 * H * HD + H * (2 * D + R + DV) + R) * qkv.element_size(), 6 * batch.T * H * R))
+
+
+def latent_attn_splits(rows, H, keys, sm_count=148, heads_per_block=32):
+    """(splits, keys per split) for a step of `rows` single-token rows over up to `keys` cache entries.  A split of a
+    sequence is one block per 32 heads (16 in the tensor-core form); about four blocks per multiprocessor hide one another's waits (a block's warps
+    walk their key tiles one behind the other), and a split is at least two key tiles long, so that fetching its
+    queries does not outweigh its keys."""
+    per_split = rows * -(-H // heads_per_block)
     tiles = -(-keys // LATENT_KEY_TILE)
-    splits = max(1, min(tiles // 4, -(-sm_count // blocks)))
+    splits = max(1, min(tiles // 2, -(-4 * sm_count // per_split)))
     chunk = -(-tiles // splits) * LATENT_KEY_TILE
     return -(-keys // chunk) if splits > 1 else 1, chunk
 
 
-def latent_attn(out, qa, gate, pool, ptab, batch, H, R, KR, scale, splits=1, chunk=0, parts=None):
+def latent_attn(out, qa, gate, pool, ptab, batch, H, R, KR, scale, splits=1, chunk=0, parts=None, tensor_cores=False):
     """Causal softmax attention of every head's query row qa [rows, H, KR + R] (float32) over the cache entries of
     its sequence (positions <= the row's own); out [rows, H, KR] (float32) = the weights' sum over the latents,
     times sigmoid(gate[t, h]) when `gate` ([rows, >= H] logits, activation dtype) is given.  `splits` > 1: the keys
     are cut into runs of `chunk` entries, each run a block of its own, merged afterwards (`parts`: float32 scratch of
-    rows * H * splits * (2 + KR))."""
+    rows * H * splits * (2 + KR)).  `tensor_cores`: a step of one token per sequence over a bfloat16 cache takes the
+    mma.sync form (the queries rounded to bfloat16, sums in float32)."""
     a = _latent_args(batch, pool, ptab, H, 0, R, KR, 0, scale=scale, qa=_ptr(qa), ldqa=qa.stride(0), gate=_ptr(gate),
                      ld_gate=0 if gate is None else gate.stride(0), out=_ptr(out), ldo=out.stride(0))
     a.splits, a.chunk, a.parts = splits, chunk, _ptr(parts)
@@ -1138,11 +1172,15 @@ def latent_attn(out, qa, gate, pool, ptab, batch, H, R, KR, scale, splits=1, chu
         raise KernelError("latent_attn: float32 queries and sums")
     if splits > 1 and (parts is None or parts.numel() < batch.T * H * splits * (2 + KR)):
         raise KernelError("latent_attn: the splits' scratch is missing or short")
-    keys = batch.max_end
-    _check(lib().cm_latent_attn(dtype_code(pool.dtype), ctypes.byref(a), _stream()), "latent_attn", 2 if splits > 1 else 1,
-           cost=lambda: (f"{batch.B} sequences, {batch.T} rows, {H} heads over {KR}+{R}",
-                         _nbytes(qa, out) + sum((p + n) * pool.shape[-1] * pool.element_size() for p, n in zip(batch.positions, batch.lengths)),
-                         sum(2 * n * H * (p + (n + 1) // 2) * (2 * KR + R) for p, n in zip(batch.positions, batch.lengths))))
+    cost = lambda: (f"{batch.B} sequences, {batch.T} rows, {H} heads over {KR}+{R}",
+                    _nbytes(qa, out) + sum((p + n) * pool.shape[-1] * pool.element_size() for p, n in zip(batch.positions, batch.lengths)),
+                    sum(2 * n * H * (p + (n + 1) // 2) * (2 * KR + R) for p, n in zip(batch.positions, batch.lengths)))
+    if tensor_cores:
+        if batch.kind != "decode" or batch.T != batch.B or pool.dtype != torch.bfloat16:
+            raise KernelError("latent_attn: the tensor-core form takes one token per sequence over a bfloat16 cache")
+        _check(lib().cm_latent_attn_mma(ctypes.byref(a), _stream()), "latent_attn_mma", 2 if splits > 1 else 1, cost=cost)
+        return
+    _check(lib().cm_latent_attn(dtype_code(pool.dtype), ctypes.byref(a), _stream()), "latent_attn", 2 if splits > 1 else 1, cost=cost)
 
 
 def head_linear(y, x, w, H, x_size, y_size):

@@ -21,8 +21,12 @@ Norms, angles, scores, softmax and the sums over the latents are float32.
 The position encoding turns the leading `position.dims` channels of the rot_dim part in interleaved pairs; further
 channels of that part pass unchanged.
 
-Every kind of step (whole prompts, portions, single tokens, mixed lengths) writes its entries to the cache first and
-then reads all keys from there, so they agree.
+Every kind of step writes its entries to the cache first.  Portions, single tokens and mixed lengths then read all
+keys from there (`kernels.latent_attn`, CUDA cores, float32 sums).  A bfloat16 step of whole prompts has a second form:
+the step's entries, kept side by side, are multiplied by [W_uk; W_uv] into keys and values per head (the turned part
+copied behind each head's key), heads padded with zeros to the 64 or 128 channels of the tensor-core attention kernels
+that the other attentions use (`Runtime.attention_prefill`).  The latents it multiplies are the bfloat16 entries that
+the cache holds, so both forms see the same keys up to the rounding of the products.
 """
 from __future__ import annotations
 
@@ -59,7 +63,13 @@ class LatentAttention(Mixer):
         self.down = Linear(names, rows, hidden)
         self.up_q = Linear(prefix + "uq", heads * (dim + rot_dim), q_rank)
         self.out = Linear(prefix + "o", hidden, heads * value_dim)
-        self.wq_norm = self.wkv_norm = self.w_uk_t = self.w_uv = self.rate = None
+        self.wq_norm = self.wkv_norm = self.w_uk_t = self.w_uv = self.w_kvu = self.rate = None
+        # the padded head of the expanded prompt form (0: heads too large for the tensor-core attention kernels)
+        need = max(dim + rot_dim, value_dim)
+        self.expand_head = 64 if need <= 64 else (128 if need <= 128 else 0)
+        # Prompts from this many tokens on take the expanded form.  Measured on B200, one prompt, 16 heads of 64 + 32 and
+        # 64 over latents of 256, CUDA-core form against expanded form: EXPAND_TABLE
+        self.expand_min_tokens = 64
 
     def children(self):
         return [self.down, self.up_q, self.out, self.position]
@@ -84,7 +94,9 @@ class LatentAttention(Mixer):
             n = min(table.numel(), self.rot_dim // 2)
             rate[:n] = table[:n]
         self.rate = rate
-        self._bound = [self.wq_norm, self.wkv_norm, self.w_uk_t, self.w_uv]
+        # [W_uk; W_uv] as stored, [H dim + H value_dim, kv_rank]: the expanded prompt form's product
+        self.w_kvu = torch.cat([tensors[p + "uk"], tensors[p + "uv"]], 0).contiguous()
+        self._bound = [self.wq_norm, self.wkv_norm, self.w_uk_t, self.w_uv, self.w_kvu]
 
     def state_spec(self):
         return KVStateSpec(1, self.entry, 0, planes=1)
@@ -95,23 +107,44 @@ class LatentAttention(Mixer):
         pool, ptab = state.pool, state.ptab
         proj = self.down.apply(rt, x)                                   # [T, QR + KR + R (+ H)]
         cq = torch.empty((T, QR), dtype=x.dtype, device=dev)
+        HD = self.expand_head
+        expand = (batch.kind == "prefill" and HD > 0 and x.dtype == torch.bfloat16 and rt.tensor_core_prompts
+                  and batch.max_len >= self.expand_min_tokens and KR % 8 == 0)
+        entries = torch.empty((T, self.entry), dtype=x.dtype, device=dev) if expand else None
         kernels.latent_prepare(cq, proj, 0, QR, self.wq_norm, self.wkv_norm, self.rate, pool, ptab, batch, H, D, R, KR, QR,
-                               self.eps)
+                               self.eps, entries=entries)
         q = self.up_q.apply(rt, cq)                                      # [T, H (D + R)]
+        if expand:
+            kvu = rt.linear(entries[:, :KR], self.w_kvu)                 # [T, H D + H DV]
+            qkv = torch.empty((T, 3 * H * HD), dtype=x.dtype, device=dev)
+            kernels.latent_expand(qkv, q, kvu, entries, self.rate, pool, ptab, batch, H, D, R, DV, KR, HD)
+            wide = torch.empty((T, H * HD), dtype=x.dtype, device=dev)
+            rt.attention_prefill(wide, qkv[:, :H * HD], qkv[:, H * HD:2 * H * HD], qkv[:, 2 * H * HD:],
+                                 proj[:, QR + KR + R:] if self.output_gate else None, batch, H, H, HD, 0, self.scale)
+            if HD == DV:
+                ctx = wide
+            else:
+                ctx = torch.empty((T, H, DV), dtype=x.dtype, device=dev)
+                ctx.copy_(wide.view(T, H, HD)[:, :, :DV])
+                ctx = ctx.view(T, H * DV)
+            return self.out.apply(rt, ctx, out_dtype=self.out_dtype)
         qa = torch.empty((T, H * (KR + R)), dtype=torch.float32, device=dev)
         kernels.head_linear(qa, q, self.w_uk_t, H, D + R, KR + R)
         if R:
             kernels.latent_query_turn(qa, q, self.rate, pool, ptab, batch, H, D, R, KR)
         sums = torch.empty((T, H * KR), dtype=torch.float32, device=dev)
         splits, chunk, parts = 1, 0, None
+        # one token per sequence over a bfloat16 cache: the heads are the rows of tensor-core products
+        mma = (batch.kind == "decode" and T == batch.B and pool.dtype == torch.bfloat16 and KR <= 512
+               and kernels.latent_decode_tensor_cores)
         if batch.kind == "decode":
             # sized by the longest sequence that the step's class of lengths allows, so that a recording serves the class
             keys = state.spec.entries(state.spec.length_class(batch.max_end))
-            splits, chunk = kernels.latent_attn_splits(T, H, keys)
+            splits, chunk = kernels.latent_attn_splits(T, H, keys, heads_per_block=16 if mma else 32)
             if splits > 1:
                 parts = rt.scratch("latent_attn_parts", T * H * splits * (2 + KR))
         kernels.latent_attn(sums, qa, proj[:, QR + KR + R:] if self.output_gate else None, pool, ptab, batch, H, R, KR,
-                            self.scale, splits=splits, chunk=chunk, parts=parts)
+                            self.scale, splits=splits, chunk=chunk, parts=parts, tensor_cores=mma)
         ctx = torch.empty((T, H * DV), dtype=x.dtype, device=dev)
         kernels.head_linear(ctx, sums, self.w_uv, H, KR, DV)
         return self.out.apply(rt, ctx, out_dtype=self.out_dtype)

@@ -285,7 +285,99 @@ def test_latent_attention_part_whole_portions_and_pages(dtype, tol, H, D, R, DV,
             _close(got, ref, tol)
 
 
-@pytest.mark.parametrize("decode", [False, True])
+@pytest.mark.parametrize("H, D, R, DV, KR, QR, W, rot_dims, head", [
+    (4, 32, 16, 64, 64, 48, 128, 16, 64), (2, 64, 32, 48, 128, 40, 96, 32, 128), (3, 24, 8, 128, 72, 24, 64, 6, 128),
+    (1, 16, 2, 16, 16, 16, 32, 2, 64)])
+def test_latent_attention_expanded_prompt_form(H, D, R, DV, KR, QR, W, rot_dims, head):
+    """Whole prompts in bfloat16, long enough for the tensor-core attention kernels of both kinds: the form that expands the
+    step's latents into keys and values per head against the form that reads the cache with the products moved to the
+    query side, and both against the plain statement.  Afterwards single tokens go on from the cache that the expanded
+    form's step wrote."""
+    from catena_models_b200 import kernels
+
+    P, m = _latent_case(11, H, D, R, DV, KR, QR, W, rot_dims)
+    P = {k: v.to(torch.bfloat16).float() for k, v in P.items()}
+    rt, part = _latent_part(P, m, W, torch.bfloat16)
+    assert part.expand_head == head
+    g = torch.Generator().manual_seed(12)
+    lengths = [1100, 65, 300]
+    xs = [torch.randn(n + 2, W, generator=g).to(torch.bfloat16).float() for n in lengths]
+    P64 = {k: v.double() for k, v in P.items()}
+    refs = [plain.latent_attention(x.double(), P64, "m.", m, 1e-5)[0] for x in xs]
+    spec = part.state_spec()
+    pages_per, slots_n = 18, 3
+    ptab = torch.randperm(slots_n * pages_per, generator=g).view(slots_n, pages_per).to(DEV, torch.int32)
+    outs = {}
+    for form, least in (("expanded", 64), ("cache", 1 << 30)):
+        part.expand_min_tokens = least
+        pool = torch.full((1, slots_n * pages_per + 1, 1, 64, spec.head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+        state = types.SimpleNamespace(pool=pool, ptab=ptab, spec=spec)
+        names = []
+        with kernels.Timeline() as tl:
+            y = part.forward(rt, _batch(lengths, [0, 0, 0], [2, 0, 1], kind="prefill"),
+                             torch.cat([x[:n] for x, n in zip(xs, lengths)]).to(DEV, torch.bfloat16), state).float().cpu()
+        names = [r["name"] for r in tl.rows()]
+        assert ("latent_expand" in names) == (form == "expanded") and ("latent_attn" in names) == (form == "cache"), names
+        outs[form] = y
+        o = 0
+        for n, ref in zip(lengths, refs):
+            _close(y[o:o + n], ref[:n], 4e-2)
+            o += n
+        # two more tokens each, one at a time, over what the step left in the cache
+        for k in range(2):
+            b = _batch([1, 1, 1], [n + k for n in lengths], [2, 0, 1], kind="decode")
+            y1 = part.forward(rt, b, torch.stack([x[n + k] for x, n in zip(xs, lengths)]).to(DEV, torch.bfloat16), state).float().cpu()
+            for i, (n, ref) in enumerate(zip(lengths, refs)):
+                _close(y1[i:i + 1], ref[n + k:n + k + 1], 2.5e-2)
+    _close(outs["expanded"], outs["cache"], 2e-2)
+
+
+@pytest.mark.parametrize("H, R, KR, positions", [
+    (5, 6, 21, [0, 1, 31, 32, 200]), (16, 16, 128, [63, 64, 700, 3, 1023]), (20, 8, 136, [500, 33]), (33, 32, 512, [90, 600, 2]),
+    (1, 2, 8, [15, 16, 17]), (12, 0, 64, [300])])
+def test_latent_attention_single_tokens_on_the_tensor_cores(H, R, KR, positions):
+    """One token per sequence over a bfloat16 cache: the tensor-core form against the float64 sum over the same entries
+    and queries (both rounded to bfloat16 beforehand, so that only the weights' rounding remains), with the keys in one
+    run and cut into runs, a gate, heads that do not fill a block of 16, latents that do not fill the warps' channels,
+    pages in any order and used pages that hold other values past each sequence's end."""
+    from catena_models_b200 import kernels
+
+    E, EC = KR + R, -(-(KR + R) // 8) * 8
+    B = len(positions)
+    g = torch.Generator().manual_seed(21)
+    per = -(-(max(positions) + 1) // 64)
+    order = torch.randperm(B * per + 2, generator=g)[:B * per].view(B, per)
+    ptab = order.to(DEV, torch.int32)
+    pool = torch.full((1, B * per + 2, 1, 64, EC), 30.0, dtype=torch.bfloat16, device=DEV)
+    entries = []
+    for b, pos in enumerate(positions):
+        lat = (torch.randn(pos + 1, E, generator=g) * 0.5).to(torch.bfloat16)
+        entries.append(lat.double())
+        for p in range(pos + 1):
+            pool[0, order[b, p // 64], 0, p % 64, :E] = lat[p].to(DEV)
+            pool[0, order[b, p // 64], 0, p % 64, E:] = 0
+    qa = (torch.randn(B, H, E, generator=g) * 0.4).to(torch.bfloat16).float()
+    gate = torch.randn(B, H + 3, generator=g).to(torch.bfloat16)
+    scale = 0.7
+    ref = torch.stack([torch.softmax(torch.einsum("he,ne->hn", qa[b].double(), entries[b]) * scale, -1) @ entries[b][:, :KR]
+                       * torch.sigmoid(gate[b, :H].double())[:, None] for b in range(B)])
+    batch = _batch([1] * B, positions, list(range(B)), kind="decode")
+    for keys in (None, 1024, 64):
+        splits, chunk, parts = 1, 0, None
+        if keys:
+            splits, chunk = kernels.latent_attn_splits(B, H, keys, heads_per_block=16)
+            parts = torch.full((B * H * splits * (2 + KR),), float("nan"), device=DEV)
+        out = torch.full((B, H * KR), float("nan"), device=DEV)
+        kernels.latent_attn(out, qa.reshape(B, H * E).to(DEV), gate.to(DEV), pool, ptab, batch, H, R, KR, scale, splits=splits,
+                            chunk=chunk, parts=parts, tensor_cores=True)
+        _close(out.view(B, H, KR), ref, 6e-3)
+        plain_out = torch.full((B, H * KR), float("nan"), device=DEV)
+        kernels.latent_attn(plain_out, qa.reshape(B, H * E).to(DEV), gate.to(DEV), pool, ptab, batch, H, R, KR, scale, splits=splits,
+                            chunk=chunk, parts=parts)
+        _close(plain_out.view(B, H, KR), ref, 2e-5)
+
+
+@pytest.mark.parametrize("decode", [False, True, "tensor cores"])
 def test_latent_attention_keys_far_away_at_borders_and_behind_the_row(decode):
     """One key is made to stand out (a query and a latent row scaled along one direction) so that the sum over the
     latents is that key's row if and only if the row sees it: keys at position 0 and 3 from far away, on both sides of
@@ -312,13 +404,20 @@ def test_latent_attention_keys_far_away_at_borders_and_behind_the_row(decode):
         direction /= direction.norm()
         keys = lat.clone()
         keys[key] += 8.0 * direction
-        pool = torch.full((1, pages + 3, 1, 64, EC), 50.0, device=DEV)       # what other sequences left in the pages
+        mma = decode == "tensor cores"
+        if mma:
+            keys = keys.to(torch.bfloat16).float()
+        pool = torch.full((1, pages + 3, 1, 64, EC), 50.0, device=DEV, dtype=torch.bfloat16 if mma else torch.float32)       # what other sequences left in the pages
         for p in range(n + 64 if not decode else row + 1):
             pool[0, order[p // 64], 0, p % 64, :E] = keys[p].to(DEV)
+            if mma:
+                pool[0, order[p // 64], 0, p % 64, E:] = 0
         qa = torch.randn(1, H, E, generator=g) * 0.3
         qa[0, 1] += 8.0 * direction                   # head 1 looks for the loud key; the others do not
+        if mma:
+            qa = qa.to(torch.bfloat16).float()
         if decode:
-            b = _batch([1], [row], [1], kind="decode") if row > 0 else _batch([1], [0], [1], kind="prefill")
+            b = _batch([1], [row], [1], kind="decode") if row > 0 or mma else _batch([1], [0], [1], kind="prefill")
             rows = qa
         else:
             # a prompt step of the rows row - 2 .. row + 1 standing on older entries; the row in question is one of them
@@ -333,10 +432,10 @@ def test_latent_attention_keys_far_away_at_borders_and_behind_the_row(decode):
             assert splits > 1
             parts = torch.full((H * splits * (2 + KR),), float("nan"), device=DEV)
         kernels.latent_attn(out, rows.reshape(b.T, H * E).to(DEV), None, pool, ptab, b, H, R, KR, 1.0, splits=splits, chunk=chunk,
-                            parts=parts)
+                            parts=parts, tensor_cores=mma)
         at = 0 if decode else row - max(0, row - 2)
         s = torch.einsum("he,ne->hn", qa[0].double(), keys[:row + 1].double())
         ref = torch.softmax(s, -1) @ keys[:row + 1, :KR].double()
-        _close(out[at].view(H, KR), ref, 2e-5)
+        _close(out[at].view(H, KR), ref, 6e-3 if mma else 2e-5)
         loud = float(torch.softmax(s, -1)[1, key]) if key <= row else 0.0
         assert (loud > 0.9) == seen, (row, key, loud)
