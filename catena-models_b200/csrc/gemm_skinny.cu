@@ -21,6 +21,8 @@ namespace cg = cooperative_groups;
 #define SK_WARPS 8
 #define SK_MODE_PLAIN 0
 #define SK_MODE_SWIGLU 1
+#define SK_MODE_GEGLU 3                      // as SWIGLU with the tanh form of gelu on the gate
+#define SK_GATED(M) ((M) == SK_MODE_SWIGLU || (M) == SK_MODE_GEGLU)
 #define SK_MODE_PARTS 2          // float partial sums per k-slice, no exchange between the blocks of a row tile
 
 __device__ __forceinline__ void mma_bf16_16816(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -108,10 +110,10 @@ gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* _
     const int g = lane >> 2, t = lane & 3;
     const int r0 = blockIdx.x * 16;
     // plain: all 8 warps split K; swiglu: warps 0-3 take the gate rows, 4-7 the up rows
-    const int splits = MODE == SK_MODE_SWIGLU ? SK_WARPS / 2 : SK_WARPS;
-    const int part = MODE == SK_MODE_SWIGLU ? (warp & 3) : warp;
-    const int row_base = (MODE == SK_MODE_SWIGLU && warp >= 4) ? N + r0 : r0;     // N = F in swiglu mode
-    const int row_limit = (MODE == SK_MODE_SWIGLU && warp >= 4) ? 2 * N : N;
+    const int splits = SK_GATED(MODE) ? SK_WARPS / 2 : SK_WARPS;
+    const int part = SK_GATED(MODE) ? (warp & 3) : warp;
+    const int row_base = (SK_GATED(MODE) && warp >= 4) ? N + r0 : r0;     // N = F in swiglu mode
+    const int row_limit = (SK_GATED(MODE) && warp >= 4) ? 2 * N : N;
     const int nblk = (K + 31) >> 5;
     const int ksplit = gridDim.y;
     const int per_cta = (nblk + ksplit - 1) / ksplit;
@@ -130,11 +132,11 @@ gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* _
         for (int j = 0; j < 4; ++j) red[warp][n][lane][j] = acc[n][j];
     __syncthreads();
     // element (n, lane, j): W row r0 + g (+8 for j >= 2), batch row 8n + 2t + (j & 1)
-    constexpr int HALVES = MODE == SK_MODE_SWIGLU ? 2 : 1;
+    constexpr int HALVES = SK_GATED(MODE) ? 2 : 1;
     __shared__ float csum[HALVES][NT * 128];
     for (int e = threadIdx.x; e < NT * 128; e += SK_WARPS * 32) {
         const int n = e >> 7, l = (e >> 2) & 31, j = e & 3;
-        if (MODE == SK_MODE_SWIGLU) {
+        if (SK_GATED(MODE)) {
             float gsum = 0.f, usum = 0.f;
 #pragma unroll
             for (int w = 0; w < 4; ++w) gsum += red[w][n][l][j];
@@ -174,9 +176,11 @@ gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* _
                 for (int r = 1; r < ksplit; ++r) tot[hlf] += cluster.map_shared_rank(&csum[hlf][0], r)[e];
             }
             if (row >= N || m >= M) continue;
-            if (MODE == SK_MODE_SWIGLU) {
+            if (SK_GATED(MODE)) {
                 const float gr = rounded<TY>(tot[0]), ur = rounded<TY>(tot[HALVES - 1]);
-                Y[(long long)m * ldy + row] = from_f32<TY>((gr * sigmoid_f32(gr)) * ur);
+                const float ag = MODE == SK_MODE_GEGLU ? 0.5f * gr * (1.f + tanhf(0.7978845608028654f * (gr + 0.044715f * gr * gr * gr)))
+                                                       : gr * sigmoid_f32(gr);
+                Y[(long long)m * ldy + row] = from_f32<TY>(ag * ur);
             } else {
                 Y[(long long)m * ldy + row] = from_f32<TY>(tot[0]);
             }
@@ -370,6 +374,7 @@ extern "C" int cm_gemm_skinny(int dty, void* Y, const void* X, const void* W, in
         CM_REFUSE("gemm_skinny: operands must be 16-byte aligned");
     if (swiglu) {
         if (dty != DT_BF16) return CM_ERR_DTYPE;
+        if (swiglu == 2) return dispatch_skinny<bf16, SK_MODE_GEGLU>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
         return dispatch_skinny<bf16, SK_MODE_SWIGLU>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
     }
     if (dty == DT_BF16) return dispatch_skinny<bf16, SK_MODE_PLAIN>(Y, X, W, M, N, K, ldx, ldw, ldy, st);

@@ -34,6 +34,15 @@ static_assert(TC_BM == CM_FEW_ROWS_MAX_ROWS, "cm_limits.h: CM_FEW_ROWS_MAX_ROWS"
 #define TCP_THREADS 320          // the persistent kernel: loader, issuer, two groups of four epilogue warps
 #define TC_MODE_PLAIN 0
 #define TC_MODE_SWIGLU 1
+#define TC_MODE_GEGLU 2                      // as SWIGLU with the tanh form of gelu on the gate
+#define TC_GATED(M) ((M) != TC_MODE_PLAIN)
+
+// What the gate passes through before it meets the up half.
+template <int MODE>
+__device__ __forceinline__ float tc_gate(float g) {
+    if (MODE == TC_MODE_GEGLU) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return __fdividef(g, 1.f + __expf(-g));
+}
 
 template <typename TC>
 __device__ __forceinline__ void store_cols(TC* dst, const float* v, int n_valid, bool aligned);
@@ -96,7 +105,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
     constexpr uint32_t B_BYTES = BLOCK_N * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr int OUT_COLS = MODE == TC_MODE_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
+    constexpr int OUT_COLS = TC_GATED(MODE) ? BLOCK_N / 2 : BLOCK_N;
     constexpr uint32_t TMEM_COLS = 2 * BLOCK_N <= 256 ? 256 : 512;    // two accumulators; allocations are powers of two
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[2 * STAGES + 4];
@@ -161,7 +170,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * TC_BK, m0);
-                if (MODE == TC_MODE_SWIGLU) {
+                if (TC_GATED(MODE)) {
                     tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * TC_BK, b0);
                     tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * TC_BK, N + b0);
                 } else {
@@ -240,13 +249,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     float v[32];
                     if (ok) {
                         tmem_load32(t_acc + (uint32_t)c, v);
-                        if (MODE == TC_MODE_SWIGLU) {
+                        if (TC_GATED(MODE)) {
                             float u[32];
                             tmem_load32(t_acc + (uint32_t)(OUT_COLS + c), u);
 #pragma unroll
                             for (int i = 0; i < 32; ++i) {
                                 const float g = rounded<TC>(v[i]), uu = rounded<TC>(u[i]);
-                                v[i] = __fdividef(g, 1.f + __expf(-g)) * uu;
+                                v[i] = tc_gate<MODE>(g) * uu;
                             }
                         }
                         if (tma_store) {
@@ -331,7 +340,7 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     constexpr uint32_t A_BYTES = A_ROWS * TC_BK * 2;
     constexpr uint32_t B_BYTES = TCS_BN * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr int OUT_COLS = MODE == TC_MODE_SWIGLU ? TCS_BN / 2 : TCS_BN;
+    constexpr int OUT_COLS = TC_GATED(MODE) ? TCS_BN / 2 : TCS_BN;
     static_assert((size_t)TCS_STAGES * STAGE_BYTES >= (size_t)A_ROWS * TCS_PITCH * 4, "staged rows must fit the ring");
     static_assert(TCS_STAGES * STAGE_BYTES <= 104 * 1024, "two blocks per SM");
     static_assert(STAGE_BYTES >= TC_BM * TC_BK * 2, "the 128-row operand read stays inside its stage");
@@ -382,7 +391,7 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const int s = i % TCS_STAGES;
         const uint32_t b_dst = tiles + s * STAGE_BYTES + A_BYTES;
         mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-        if (MODE == TC_MODE_SWIGLU) {
+        if (TC_GATED(MODE)) {
             tma_load_2d(b_dst, &map_b, full0 + 8 * s, (kb0 + i) * TC_BK, n0);
             tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, (kb0 + i) * TC_BK, N + n0);
         } else {
@@ -483,7 +492,7 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             }
         }
     } else {
-        const int col = n0 + (MODE == TC_MODE_SWIGLU ? (lane & 15) * 4 : lane * 4);
+        const int col = n0 + (TC_GATED(MODE) ? (lane & 15) * 4 : lane * 4);
         const bool vec_ok = (ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
         constexpr int ROW_STEP = TC_THREADS / 32;
         for (int row0 = rank + splits * warp; row0 < M; row0 += 2 * splits * ROW_STEP) {
@@ -515,12 +524,12 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 }
             }
             float o[4] = {acc.x, acc.y, acc.z, acc.w};
-            if (MODE == TC_MODE_SWIGLU) {
+            if (TC_GATED(MODE)) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const float u = rounded<TC>(__shfl_down_sync(0xffffffffu, o[i], 16));
                     const float g = rounded<TC>(o[i]);
-                    o[i] = __fdividef(g, 1.f + __expf(-g)) * u;
+                    o[i] = tc_gate<MODE>(g) * u;
                 }
                 if (lane >= 16) continue;
             }
@@ -590,14 +599,14 @@ static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K,
                      long long ldc, int* err, cudaStream_t st, int ksplit = 1, long long part_stride = 0,
                      const int* tile_group = nullptr, int groups = 1) {
     CUtensorMap map_a, map_b;
-    const int group_rows = MODE == TC_MODE_SWIGLU ? 2 * N : N;
+    const int group_rows = TC_GATED(MODE) ? 2 * N : N;
     const long long b_rows = (long long)groups * group_rows;
-    const int b_box = MODE == TC_MODE_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
+    const int b_box = TC_GATED(MODE) ? BLOCK_N / 2 : BLOCK_N;
     int rc = make_map(&map_a, A, M, K, lda, TC_BM);
     if (rc != CM_OK) return rc;
     rc = make_map(&map_b, B, b_rows, K, ldb, b_box);
     if (rc != CM_OK) return rc;
-    constexpr int OUT_COLS = MODE == TC_MODE_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
+    constexpr int OUT_COLS = TC_GATED(MODE) ? BLOCK_N / 2 : BLOCK_N;
     static_assert(OUT_COLS % (128 / (int)sizeof(TC)) == 0, "a tile is a whole number of staged pieces");
     // TMA stores want a 16-byte aligned base and pitch; other outputs are stored from registers
     CUtensorMap map_c = map_a;
@@ -664,7 +673,7 @@ template <typename TC, int MODE, int A_ROWS, int STAGES>
 static int launch_splitk_rows(void* C, const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
                          long long ldc, int force_splits, int* err, cudaStream_t st, float* parts = nullptr,
                          long long part_stride = 0) {
-    constexpr int OUT_COLS = MODE == TC_MODE_SWIGLU ? TCS_BN / 2 : TCS_BN;
+    constexpr int OUT_COLS = TC_GATED(MODE) ? TCS_BN / 2 : TCS_BN;
     const size_t smem = (size_t)STAGES * (A_ROWS * TC_BK * 2 + TCS_BN * TC_BK * 2) + 1024;
     auto kernel = gemm_tc_splitk_kernel<TC, MODE, A_ROWS, STAGES>;
     static bool configured = false;
@@ -697,8 +706,8 @@ static int launch_splitk_rows(void* C, const void* A, const void* B, int M, int 
         // for fewer rows and blocks only (us, split two ways / unsplit in the persistent kernel): 72 tiles of a
         // 9,216 x 1,024 matrix 8.1 / 9.9 at 32 rows, 9.1 / 10.0 at 64, 12.1 / 10.1 at 128; 128 tiles of a
         // 16,384 x 2,048 matrix 14.6 / 16.0 at 32 rows, 21.4 / 16.2 at 64.
-        const int budget = MODE != TC_MODE_SWIGLU ? 7 * sm_count / 5 : M <= 32 ? 2 * sm_count : M <= 64 ? sm_count : sm_count / 4;
-        for (int s = MODE == TC_MODE_SWIGLU ? 2 : 8; s >= 2; --s) {       // SwiGLU: two ways at most (four: 10.7 against 7.4 us)
+        const int budget = !TC_GATED(MODE) ? 7 * sm_count / 5 : M <= 32 ? 2 * sm_count : M <= 64 ? sm_count : sm_count / 4;
+        for (int s = TC_GATED(MODE) ? 2 : 8; s >= 2; --s) {       // SwiGLU: two ways at most (four: 10.7 against 7.4 us)
             if (4 * s > num_kb || n_tiles * s > budget) continue;
             if (splitk_active_clusters<TC, MODE, A_ROWS, STAGES>(s, smem) > 0) {
                 splits = s;
@@ -716,7 +725,7 @@ static int launch_splitk_rows(void* C, const void* A, const void* B, int M, int 
     CUtensorMap map_a, map_b;
     int rc = make_map(&map_a, A, M, K, lda, A_ROWS);
     if (rc != CM_OK) return rc;
-    rc = make_map(&map_b, B, MODE == TC_MODE_SWIGLU ? 2LL * N : N, K, ldb, MODE == TC_MODE_SWIGLU ? TCS_BN / 2 : TCS_BN);
+    rc = make_map(&map_b, B, TC_GATED(MODE) ? 2LL * N : N, K, ldb, TC_GATED(MODE) ? TCS_BN / 2 : TCS_BN);
     if (rc != CM_OK) return rc;
     // with `parts` the k-slices are independent blocks (no cluster): each leaves its sums in parts[slice]
     cm_launch_cluster(kernel, dim3(n_tiles, splits), TC_THREADS, smem, st, parts ? 1 : splits, true, map_a, map_b, (TC*)C,
@@ -741,6 +750,10 @@ extern "C" int cm_gemm_tc(int dtc, void* C, const void* A, const void* B, int M,
     if (block_n == 192 && (swiglu || dtc != DT_BF16)) CM_REFUSE("gemm_tc: 192-wide tiles are for plain bfloat16 products");
     if (swiglu) {
         if (dtc != DT_BF16) return CM_ERR_DTYPE;
+        if (swiglu == 2) {
+            if (block_n == 256) return launch_tc<256, 4, bf16, TC_MODE_GEGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
+            return launch_tc<128, 6, bf16, TC_MODE_GEGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
+        }
         if (block_n == 256) return launch_tc<256, 4, bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
         return launch_tc<128, 6, bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     }
@@ -766,6 +779,7 @@ extern "C" int cm_gemm_tc_grouped(int dtc, void* C, const void* A, const void* B
         CM_REFUSE("gemm_tc_grouped: operands must be 16-byte aligned");
     if (!tile_group || groups < 1) CM_REFUSE("gemm_tc_grouped: the row tiles' groups are missing");
     if (block_n != 128 && block_n != 256) CM_REFUSE("gemm_tc_grouped: tile width %d (128 or 256)", block_n);
+    if (swiglu == 2) CM_REFUSE("gemm_tc_grouped: the gated form has silu only");
     if (swiglu) {
         if (dtc != DT_BF16) return CM_ERR_DTYPE;
         if (block_n == 256)
@@ -845,7 +859,8 @@ extern "C" int cm_gemm_tc_few_rows(int dtc, void* C, const void* A, const void* 
     int rc;
     if (swiglu) {
         if (dtc != DT_BF16) return CM_ERR_DTYPE;
-        rc = launch_splitk<bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, splits, err, st);
+        rc = swiglu == 2 ? launch_splitk<bf16, TC_MODE_GEGLU>(C, A, B, M, N, K, lda, ldb, ldc, splits, err, st)
+                         : launch_splitk<bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, splits, err, st);
     } else if (dtc == DT_BF16) {
         rc = launch_splitk<bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, splits, err, st);
     } else if (dtc == DT_F32) {

@@ -2,9 +2,11 @@
 // 16 heads against a tile of cache entries and for the weights' product with the same entries' latents.
 //
 // All heads of a sequence meet the same entries, so the heads are the rows of the products: one block = one sequence,
-// one run of keys (a split) and 16 heads.  A tile is LM_KT entries, copied whole (cp.async) into shared memory rows
-// padded by 16 bytes.  Every one of the four warps forms the tile's scores [16 heads x LM_KT keys] over all E = KR + R
-// channels for itself (so the warps exchange nothing), masks, keeps the running maximum and sum in float, and adds
+// one run of keys (a split) and 16 heads.  A tile is LM_KT = 32 entries, copied whole (cp.async) into shared memory
+// rows padded by 16 bytes; the next tile is copied into a second buffer while the present one is multiplied.  Each of
+// the four warps forms the scores of the 16 heads against eight of the tile's keys over all E = KR + R channels and
+// leaves them in shared memory; then every warp takes the whole tile's scores [16 x LM_KT], masks, keeps the running
+// maximum and sum in float (each warp for itself: the same numbers in all four), and adds
 // P [16 x LM_KT] x latents [LM_KT x its own quarter of the KR channels] to its output tile in registers.  The queries
 // come as float rows [W_uk^T q_plain | q_turn] and are rounded to bfloat16 on their way into shared memory; the scale
 // multiplies the float scores.  Splits leave (maximum, sum, unnormalised sums) as the CUDA-core form does, and the same
@@ -16,16 +18,16 @@
 #define LM_KT 32
 #define LM_THREADS 128
 #define LM_PAD 8
+#define LM_LDS (LM_KT + 8)                     // pitch (floats) of the tile's scores in shared memory
 
 __device__ __forceinline__ void lm_copy16(void* dst, const void* src, bool valid) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
     const int n = valid ? 16 : 0;                 // 0 source bytes: the 16 destination bytes are zero-filled
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
 }
-__device__ __forceinline__ void lm_copy_wait() {
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-}
+__device__ __forceinline__ void lm_copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void lm_copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void lm_ldsm_x4(uint32_t* r, const void* p) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -53,9 +55,9 @@ __device__ __forceinline__ uint32_t lm_pack(float lo, float hi) {
 }
 
 // The pitches (elements) of a query row and of an entry in shared memory.  EP: the channels the score products walk
-// (E up to a multiple of 16; what lies behind E is zeros on both sides); an entry's row also covers the 4 * NT * 8
+// (E up to a multiple of 32; what lies behind E is zeros on both sides); an entry's row also covers the 4 * NT * 8
 // channels that the warps' output tiles span.  Both are odd multiples of 16 bytes: ldmatrix meets no bank twice.
-static inline int lm_ep(int E) { return (E + 15) & ~15; }
+static inline int lm_ep(int E) { return (E + 31) & ~31; }
 static inline int lm_ldk(int E, int nt) { return max(lm_ep(E), 4 * nt * 8) + LM_PAD; }
 
 // NT: output tiles of 8 channels per warp (4 warps x NT x 8 >= KR).
@@ -67,19 +69,21 @@ latent_attn_mma_kernel(const LatentArgs a) {
     pdl_wait();
     const int b = blockIdx.z, split = blockIdx.y, hg = blockIdx.x;
     const int H = a.H, E = a.E, KR = a.KR, EC = a.EC;
-    const int EP = (E + 15) & ~15, LDQ = EP + LM_PAD, LDK = max(EP, 4 * NT * 8) + LM_PAD;
+    const int EP = (E + 31) & ~31, LDQ = EP + LM_PAD, LDK = max(EP, 4 * NT * 8) + LM_PAD;
     bf16* Qs = reinterpret_cast<bf16*>(lm_smem);          // [16][LDQ]
-    bf16* Ks = Qs + 16 * LDQ;                             // [LM_KT][LDK]
+    bf16* Ks = Qs + 16 * LDQ;                             // [2][LM_KT][LDK]
+    float* Ss = reinterpret_cast<float*>(Ks + 2 * LM_KT * LDK);      // [16][LM_LDS]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const long long t = a.seq_start[b];                   // the sequence's one row of the step
     const int pos = a.seq_pos0[b], end = a.seq_end[b];
-    // the 16 heads' queries, rounded; zeros for heads past H and channels past E
-    for (int e = tid; e < 16 * LDQ; e += LM_THREADS) {
-        const int m = e / LDQ, c = e - m * LDQ, h = hg * 16 + m;
-        Qs[e] = __float2bfloat16_rn((h < H && c < E) ? a.qa[t * a.ldqa + (long long)h * E + c] : 0.f);
+    // the 16 heads' queries, rounded; zeros for heads past H and channels past E (eight threads a head)
+    {
+        const int m = tid >> 3, h = hg * 16 + m;
+        const float* src = a.qa + t * a.ldqa + (long long)h * E;
+        for (int c = tid & 7; c < LDQ; c += 8) Qs[m * LDQ + c] = __float2bfloat16_rn((h < H && c < E) ? src[c] : 0.f);
     }
     // what no copy writes (channels from EC on) is zeros once and for all
-    for (int e = tid; e < LM_KT * (LDK - EC); e += LM_THREADS) {
+    for (int e = tid; e < 2 * LM_KT * (LDK - EC); e += LM_THREADS) {
         const int j = e / (LDK - EC), c = EC + e - j * (LDK - EC);
         Ks[j * LDK + c] = __float2bfloat16_rn(0.f);
     }
@@ -95,33 +99,58 @@ latent_attn_mma_kernel(const LatentArgs a) {
     const int* ptab = a.ptab + (long long)a.seq_slot[b] * a.ptab_stride;
     const int C8 = EC >> 3;
     const int ch0 = warp * NT * 8;                        // the warp's first output channel
-    for (int k0 = k_first; k0 <= k_last; k0 += LM_KT) {
-        __syncthreads();                                  // the tile before is no longer read (and the queries are in place)
-        for (int e = tid; e < LM_KT * C8; e += LM_THREADS) {
-            const int j = e / C8, c = (e - j * C8) * 8, kp = k0 + j;
-            const bool valid = kp < end && kp <= k_last;
-            const bf16* src = (const bf16*)a.pool +
-                              (valid ? ((long long)ptab[kp / PAGE_TOKENS] * PAGE_TOKENS + kp % PAGE_TOKENS) * EC + c : 0);
-            lm_copy16(Ks + j * LDK + c, src, valid);
+    // A tile's entries into buffer `buf`, 16 bytes a copy, four threads an entry; entries at or behind the sequence's end
+    // become zeros.  A tile starts at a multiple of LM_KT and so lies within one page: its page index is read from the
+    // table a round ahead, and no copy waits for a load.
+    static_assert(PAGE_TOKENS % LM_KT == 0 && LM_THREADS == 4 * LM_KT, "a tile within a page, four threads an entry");
+    auto fetch = [&](int k0, int buf, int page) {
+        const int j = tid >> 2, kp = k0 + j;
+        const bool valid = kp < end && kp <= k_last;
+        const bf16* src = (const bf16*)a.pool + (valid ? ((long long)page * PAGE_TOKENS + kp % PAGE_TOKENS) * EC : 0);
+        bf16* dst = Ks + (buf * LM_KT + j) * LDK;
+        for (int c8 = tid & 3; c8 < C8; c8 += 4) lm_copy16(dst + c8 * 8, src + (valid ? c8 * 8 : 0), valid);
+        lm_copy_commit();
+    };
+    const bool any = k_first <= k_last;
+    int page_next = 0;
+    if (any) {
+        fetch(k_first, 0, ptab[k_first / PAGE_TOKENS]);
+        if (k_first + LM_KT <= k_last) page_next = ptab[(k_first + LM_KT) / PAGE_TOKENS];
+    }
+    int buf = 0;
+    for (int k0 = k_first; k0 <= k_last; k0 += LM_KT, buf ^= 1) {
+        // the other buffer's tile was multiplied before the barrier that ended the round before this one
+        const bool more = k0 + LM_KT <= k_last;
+        if (more) {
+            fetch(k0 + LM_KT, buf ^ 1, page_next);
+            if (k0 + 2 * LM_KT <= k_last) page_next = ptab[(k0 + 2 * LM_KT) / PAGE_TOKENS];
         }
-        lm_copy_wait();
+        if (more) lm_copy_wait<1>(); else lm_copy_wait<0>();
+        __syncthreads();                                  // every thread's copies of this tile (and the queries) are in place
+        const bf16* Kt = Ks + buf * LM_KT * LDK;
+        // ---- scores of the 16 heads against the warp's eight keys of the tile, over all channels; two steps of 16
+        //      channels a matrix load of the keys
+        {
+            float sw[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int kk = 0; kk < EP / 32; ++kk) {
+                uint32_t kb[4], qf[4];
+                lm_ldsm_x4(kb, Kt + (warp * 8 + (lane & 7)) * LDK + kk * 32 + 8 * (lane >> 3));
+                lm_ldsm_x4(qf, Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDQ + kk * 32 + 8 * (lane >> 4));
+                lm_mma(sw, qf, kb[0], kb[1]);
+                lm_ldsm_x4(qf, Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDQ + kk * 32 + 16 + 8 * (lane >> 4));
+                lm_mma(sw, qf, kb[2], kb[3]);
+            }
+            *reinterpret_cast<float2*>(Ss + g * LM_LDS + warp * 8 + 2 * t4) = make_float2(sw[0], sw[1]);
+            *reinterpret_cast<float2*>(Ss + (g + 8) * LM_LDS + warp * 8 + 2 * t4) = make_float2(sw[2], sw[3]);
+        }
         __syncthreads();
-        // ---- scores of the 16 heads against the tile's keys
+        // every warp takes all of the tile's scores, laid out as the products leave them
         float s[LM_KT / 8][4];
 #pragma unroll
-        for (int j = 0; j < LM_KT / 8; ++j)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) s[j][i] = 0.f;
-        for (int kk = 0; kk < EP / 16; ++kk) {
-            uint32_t qf[4];
-            lm_ldsm_x4(qf, Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDQ + kk * 16 + 8 * (lane >> 4));
-#pragma unroll
-            for (int jp = 0; jp < LM_KT / 16; ++jp) {     // key tiles 2jp, 2jp + 1
-                uint32_t kb[4];
-                lm_ldsm_x4(kb, Ks + (jp * 16 + (lane & 7) + 8 * (lane >> 4)) * LDK + kk * 16 + 8 * ((lane >> 3) & 1));
-                lm_mma(s[2 * jp], qf, kb[0], kb[1]);
-                lm_mma(s[2 * jp + 1], qf, kb[2], kb[3]);
-            }
+        for (int j = 0; j < LM_KT / 8; ++j) {
+            const float2 lo = *reinterpret_cast<const float2*>(Ss + g * LM_LDS + j * 8 + 2 * t4);
+            const float2 hi = *reinterpret_cast<const float2*>(Ss + (g + 8) * LM_LDS + j * 8 + 2 * t4);
+            s[j][0] = lo.x; s[j][1] = lo.y; s[j][2] = hi.x; s[j][3] = hi.y;
         }
         // ---- mask (every head stands at the same position), running maximum
         float mx[2] = {-INFINITY, -INFINITY};
@@ -169,11 +198,12 @@ latent_attn_mma_kernel(const LatentArgs a) {
 #pragma unroll
             for (int dp = 0; dp < NT / 2; ++dp) {         // channel tiles 2dp, 2dp + 1
                 uint32_t vb[4];
-                lm_ldsm_x4_trans(vb, Ks + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDK + ch0 + dp * 16 + 8 * (lane >> 4));
+                lm_ldsm_x4_trans(vb, Kt + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDK + ch0 + dp * 16 + 8 * (lane >> 4));
                 lm_mma(o[2 * dp], pf[kk], vb[0], vb[1]);
                 lm_mma(o[2 * dp + 1], pf[kk], vb[2], vb[3]);
             }
         }
+        __syncthreads();                                  // this buffer is refilled in the next round
     }
     // ---- the rows' sums over the quad, then parts or the finished rows
 #pragma unroll
@@ -222,7 +252,7 @@ extern "C" int cm_latent_attn_mma(const LatentArgs* args, cudaStream_t st) {
     if (a.splits < 1 || (a.splits > 1 && (!a.parts || a.chunk < LM_KT || a.chunk % LM_KT)))
         CM_REFUSE("latent_attn_mma: %d splits of %d keys", a.splits, a.chunk);
     const int nt = a.KR <= 128 ? 4 : (a.KR <= 256 ? 8 : 16);
-    const size_t smem = (size_t)(16 * (lm_ep(a.E) + LM_PAD) + LM_KT * lm_ldk(a.E, nt)) * sizeof(bf16);
+    const size_t smem = (size_t)(16 * (lm_ep(a.E) + LM_PAD) + 2 * LM_KT * lm_ldk(a.E, nt)) * sizeof(bf16) + 16 * LM_LDS * sizeof(float);
     dim3 grid((unsigned)((a.H + 15) / 16), a.splits, a.B);
 #define LM_LAUNCH(N)                                                                                               \
     do {                                                                                                           \

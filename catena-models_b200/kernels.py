@@ -434,9 +434,13 @@ def gemm_simt(y, x, w):
            cost=lambda: (f"{M}x{N}x{K}", _nbytes(x, w, y), 2 * M * N * K))
 
 
+_GATE_SUFFIX = ("", "_swiglu", "_geglu")     # a product's name by its gate flag
+
+
 def gemm_skinny(y, x, w, swiglu=False):
     """y = x @ w^T for at most 64 bfloat16 rows, weights streamed once (mma.sync, float sums).
-    swiglu: w is [gate; up] with 2F rows and y[M, F] = silu(x Wgate^T) * (x Wup^T)."""
+    swiglu: w is [gate; up] with 2F rows and y[M, F] = silu(x Wgate^T) * (x Wup^T); swiglu=2 (all three products that
+    take the flag): the tanh form of gelu in silu's place."""
     _need_cuda(y, x, w)
     M, K = x.shape
     N = y.shape[1]
@@ -444,13 +448,14 @@ def gemm_skinny(y, x, w, swiglu=False):
         raise KernelError(f"gemm_skinny shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_skinny takes bfloat16 operands")
-    if _fusable_rows(x, w) and y.stride(1) == 1 and (y.dtype == torch.bfloat16 or (y.dtype == torch.float32 and not swiglu)):
+    if (_fusable_rows(x, w) and y.stride(1) == 1 and int(swiglu) < 2
+            and (y.dtype == torch.bfloat16 or (y.dtype == torch.float32 and not swiglu))):
         mode = FD_SWIGLU if swiglu else (FD_PLAIN if y.dtype == torch.bfloat16 else FD_F32)
         _fuser.add((y, x, w), kind=FD_GEMV, mode=mode, M=M, N=N, K=K, ksplit=1, ldx=x.stride(0), ldw=w.stride(0),
                    ldy=y.stride(0), x=_ptr(x), w=_ptr(w), y=_ptr(y))
         return
     _check(lib().cm_gemm_skinny(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0),
-                                y.stride(0), int(swiglu), _stream()), "gemm_skinny" + ("_swiglu" if swiglu else ""),
+                                y.stride(0), int(swiglu), _stream()), "gemm_skinny" + _GATE_SUFFIX[int(swiglu)],
            cost=lambda: (f"{M}x{w.shape[0]}x{K}", _nbytes(x, w, y), 2 * M * w.shape[0] * K))
 
 
@@ -521,7 +526,7 @@ def gemm_tc(y, x, w, swiglu=False, err=None, block_n=256):
     if x.stride(1) != 1 or w.stride(1) != 1 or y.stride(1) != 1:
         raise KernelError("gemm_tc takes row-major operands")
     _check(lib().cm_gemm_tc(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0),
-                            y.stride(0), int(swiglu), block_n, _ptr(err), _stream()), "gemm_tc" + ("_swiglu" if swiglu else ""),
+                            y.stride(0), int(swiglu), block_n, _ptr(err), _stream()), "gemm_tc" + _GATE_SUFFIX[int(swiglu)],
            cost=lambda: (f"{M}x{w.shape[0]}x{K}", _nbytes(x, w, y), 2 * M * w.shape[0] * K))
 
 
@@ -540,7 +545,7 @@ def gemm_tc_few_rows(y, x, w, swiglu=False, err=None, splits=0):
         raise KernelError("gemm_tc_few_rows takes row-major operands")
     _check(lib().cm_gemm_tc_few_rows(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0),
                                      w.stride(0), y.stride(0), int(swiglu), splits, _ptr(err), _stream()),
-           "gemm_tc_few_rows" + ("_swiglu" if swiglu else ""),
+           "gemm_tc_few_rows" + _GATE_SUFFIX[int(swiglu)],
            cost=lambda: (f"{M}x{w.shape[0]}x{K}", _nbytes(x, w, y), 2 * M * w.shape[0] * K))
 
 

@@ -23,7 +23,7 @@ class SwiGLU(FeedForward):
             raise ValueError("SwiGLU: activation silu|gelu_tanh")
         self.gelu = activation == "gelu_tanh"
         if self.gelu:
-            self.fused_decode_ok = False         # the products' fused silu epilogue is not this activation
+            self.fused_decode_ok = False         # the persistent decode kernel's gated product has silu only
         self.out_dtype = {None: None, "float32": torch.float32}[out_dtype]
         names = names or {}
         n = lambda key, default: prefix + names.get(key, default)
@@ -36,14 +36,7 @@ class SwiGLU(FeedForward):
         return [self.gate_up, self.down]
 
     def forward(self, rt, batch, x):
-        if self.gelu:
-            from .. import kernels
-            import torch
-
-            a = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
-            kernels.swiglu(a, self.gate_up.apply(rt, x), gelu=True)
-        else:
-            a = rt.gate_up_swiglu(x, self.gate_up.weight, self.intermediate)
+        a = rt.gate_up_swiglu(x, self.gate_up.weight, self.intermediate, gelu=self.gelu)
         return self.down.apply(rt, a, out_dtype=self.out_dtype, partial_ok=batch.partial_sums_ok and self.out_dtype is None)
 
 

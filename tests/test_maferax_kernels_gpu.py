@@ -88,6 +88,33 @@ def test_tanh_gelu_gate():
 
 
 # ------------------------------------------------------------------------------ gated linear attention
+@pytest.mark.parametrize("rows", [1, 8, 40, 128, 300])
+def test_tanh_gelu_gate_in_the_products(rows):
+    """The gate in the epilogue of the three bfloat16 products against act(g) * u of the rounded halves in float64."""
+    from catena_models_b200 import kernels
+
+    g = torch.Generator().manual_seed(rows)
+    K, F = 256, 384
+    x = (torch.randn(rows, K, generator=g)).to(torch.bfloat16)
+    w = (torch.randn(2 * F, K, generator=g) * 0.12).to(torch.bfloat16)
+    gu = (x.double() @ w.double().t()).to(torch.bfloat16).double()
+    ref = plain.gelu_tanh(gu[:, :F]) * gu[:, F:]
+    xd, wd = x.to(DEV), w.to(DEV)
+    forms = [kernels.gemm_tc]
+    if rows <= 128:
+        forms.append(kernels.gemm_tc_few_rows)
+    if rows <= 64:
+        forms.append(kernels.gemm_skinny)
+    for form in forms:
+        a = torch.full((rows, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+        form(a, xd, wd, swiglu=2)
+        torch.cuda.synchronize()
+        _close(a, ref, 1e-2)
+        silu = torch.empty_like(a)
+        form(silu, xd, wd, swiglu=True)
+        _close(silu, torch.nn.functional.silu(gu[:, :F]) * gu[:, F:], 1e-2)
+
+
 @pytest.mark.parametrize("tau", [1.0, 16.0])
 def test_decay_of_gated_linear_attention_both_forms(tau):
     from catena_models_b200 import kernels
