@@ -579,6 +579,41 @@ def maferax_config(size, vocab=VOCAB):
                 layers=layers)
 
 
+def latent_decode_table(pk, device="cuda:0", cases=((8, 16, 256, 32), (128, 16, 256, 32), (64, 32, 512, 32)), held=2048):
+    """`--latent-table`: the single-token latent attention alone, in its tensor-core and its CUDA-core form: `B` sequences
+    that hold `held` tokens, `H` heads over latents of `KR` + `R` channels, random bfloat16 entries in pages laid out in
+    any order, launched for a length class of twice `held`.  Bytes: every sequence's cache entries once."""
+    import types
+
+    import torch
+
+    from catena_models_b200 import kernels as K
+
+    print(f"\n### single-token latent attention alone, {held} held tokens, bfloat16 cache\n")
+    print(f"| sequences | heads | latent + turned | form | splits x keys | us | GB/s of cache entries | of copy ({pk['hbm_gbs']:.0f}) |")
+    print("|---|---|---|---|---|---|---|---|")
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+    for B, H, KR, R in cases:
+        E = KR + R
+        per = held // 64 + 1
+        pool = (torch.randn(1, B * per, 1, 64, E, device=device) * 0.5).to(torch.bfloat16)
+        ptab = torch.randperm(B * per, device=device).view(B, per).to(torch.int32)
+        qa = torch.randn(B, H * E, device=device) * 0.3
+        gate = torch.randn(B, H, device=device).to(torch.bfloat16)
+        out = torch.empty(B, H * KR, device=device)
+        batch = types.SimpleNamespace(tok_seq=i32(list(range(B))), tok_pos=i32([held] * B), seq_start=i32(list(range(B + 1))),
+                                      seq_pos0=i32([held] * B), seq_end=i32([held + 1] * B), seq_slot=i32(list(range(B))), B=B,
+                                      T=B, max_len=1, max_end=held + 1, positions=[held] * B, lengths=[1] * B, kind="decode")
+        for tc in (True, False):
+            splits, chunk = K.latent_attn_splits(B, H, 2 * held, heads_per_block=16 if tc else 32, kv_rank=KR)
+            parts = torch.empty(B * H * splits * (2 + KR), device=device) if splits > 1 else None
+            us = _graph_time_us(torch, lambda: K.latent_attn(out, qa, gate, pool, ptab, batch, H, R, KR, E ** -0.5, splits=splits,
+                                                             chunk=chunk, parts=parts, tensor_cores=tc))
+            gbs = B * (held + 1) * E * 2 / (us * 1e-6) / 1e9
+            print(f"| {B} | {H} | {KR} + {R} | {'mma.sync' if tc else 'CUDA cores'} | {splits} x {chunk} | {us:.1f} | {gbs:.0f} | "
+                  f"{gbs / pk['hbm_gbs']:.2f} |", flush=True)
+
+
 def lfm3_like_config(size, vocab=VOCAB):
     z = COMPARE_SIZES[size]
     return dict(architecture="lfm3", vocab_size=vocab, hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=8,
@@ -712,6 +747,8 @@ def main():
                     help="time one decode step and one prompt step kernel by kernel and print the table")
     ap.add_argument("--attention-table", action="store_true",
                     help="time the prompt-attention kernels alone at 2,048, 4,096 and 16,384 tokens and print the table")
+    ap.add_argument("--latent-table", action="store_true",
+                    help="instead of the JSON line: time the single-token latent attention alone, tensor-core and CUDA-core form")
     ap.add_argument("--compare", default=None, choices=["narasun", "fozedra", "maferax"],
                     help="instead of the JSON line: prompt and decode throughput of that design beside the closest earlier "
                          "one at equal size (random weights: Narasun beside LFM3, Fozedra and Maferax beside Narasun), as a table")
@@ -728,6 +765,9 @@ def main():
         print(json.dumps({"impl": "reference", "unavailable":
                           "catena-models is a Rust crate whose kernel compiler is a network git dependency; "
                           "no Rust toolchain, no network and no GGUF checkpoint here, and pip finds no Python project in it"}))
+        return 0
+    if args.latent_table and args.gpus == 1:
+        latent_decode_table(peaks())
         return 0
     if args.compare and args.gpus == 1:
         compare_designs(args.compare, args.compare_sizes.split(","), args.prompt_len or 2048, args.batch or 8, min(args.steps, 64), peaks(),

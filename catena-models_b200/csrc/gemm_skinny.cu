@@ -178,8 +178,9 @@ gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* _
             if (row >= N || m >= M) continue;
             if (SK_GATED(MODE)) {
                 const float gr = rounded<TY>(tot[0]), ur = rounded<TY>(tot[HALVES - 1]);
-                const float ag = MODE == SK_MODE_GEGLU ? 0.5f * gr * (1.f + tanhf(0.7978845608028654f * (gr + 0.044715f * gr * gr * gr)))
-                                                       : gr * sigmoid_f32(gr);
+                float th = 0.f;      // the hardware's tanh, as in the tensor-core products' epilogue: the same digits from every product
+                if (MODE == SK_MODE_GEGLU) asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.7978845608028654f * (gr + 0.044715f * gr * gr * gr)));
+                const float ag = MODE == SK_MODE_GEGLU ? 0.5f * gr * (1.f + th) : gr * sigmoid_f32(gr);
                 Y[(long long)m * ldy + row] = from_f32<TY>(ag * ur);
             } else {
                 Y[(long long)m * ldy + row] = from_f32<TY>(tot[0]);

@@ -40,7 +40,12 @@ static_assert(TC_BM == CM_FEW_ROWS_MAX_ROWS, "cm_limits.h: CM_FEW_ROWS_MAX_ROWS"
 // What the gate passes through before it meets the up half.
 template <int MODE>
 __device__ __forceinline__ float tc_gate(float g) {
-    if (MODE == TC_MODE_GEGLU) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    if (MODE == TC_MODE_GEGLU) {
+        // the hardware's tanh (to about 2^-11 of its value; the result is rounded to bfloat16, 2^-9, right after)
+        float th;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+        return 0.5f * g * (1.f + th);
+    }
     return __fdividef(g, 1.f + __expf(-g));
 }
 

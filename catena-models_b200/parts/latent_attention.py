@@ -140,7 +140,7 @@ class LatentAttention(Mixer):
         if batch.kind == "decode":
             # sized by the longest sequence that the step's class of lengths allows, so that a recording serves the class
             keys = state.spec.entries(state.spec.length_class(batch.max_end))
-            splits, chunk = kernels.latent_attn_splits(T, H, keys, heads_per_block=16 if mma else 32)
+            splits, chunk = kernels.latent_attn_splits(T, H, keys, heads_per_block=16 if mma else 32, kv_rank=KR)
             if splits > 1:
                 parts = rt.scratch("latent_attn_parts", T * H * splits * (2 + KR))
         kernels.latent_attn(sums, qa, proj[:, QR + KR + R:] if self.output_gate else None, pool, ptab, batch, H, R, KR,
