@@ -564,18 +564,18 @@ def maferax_config(size, vocab=VOCAB):
     Narasun model above: four layers of gated linear attention (the matrix memory's head sizes, a decay network of the decay
     mix's rank) and four of latent attention (the attention's heads; a latent of a quarter of the width plus a turned part of
     32 channels per token instead of keys and values per head), dense and routed feed-forwards in turn; the router has
-    four identity experts beside the real ones, three groups of which two stay open."""
+    two identity experts beside the real ones, in two groups of which one stays open."""
     z = COMPARE_SIZES[size]
-    lin = lambda mlp: dict(type="gla", mlp=mlp, mixer=dict(heads=z["mem_heads"], dim=z["mem_dim"], vdim=z["mem_vdim"], tau=16.0,
+    lin = lambda mlp: dict(type="gla", mlp=mlp, mixer=dict(heads=z["mem_heads"], dim=z["mem_dim"], vdim=z["mem_vdim"], tau=8.0,
                                                            rank=z["rank"]))
     lat = lambda mlp: dict(type="latent_attention", mlp=mlp, mixer=dict(
         heads=z["heads"], dim=z["head"], rot_dim=32, vdim=z["head"], kv_rank=z["width"] // 4, q_rank=3 * z["width"] // 8,
         scale=(z["head"] + 32) ** -0.5, rot=dict(dims=32, base=1000000.0)))
     dense = dict(kind="dense", ff=z["ff"])
     moe = dict(kind="moe", expert=dict(ff=z["expert_ff"]),
-               router=dict(experts=z["experts"], top=z["top"], identity=4, scale=2.0, groups=dict(count=3, keep=2)))
+               router=dict(experts=z["experts"], top=z["top"], identity=2, scale=1.5, groups=dict(count=2, keep=1)))
     layers = [lin(dense), lat(moe), lin(moe), lat(dense), lin(dense), lat(moe), lin(moe), lat(dense)]
-    return dict(architecture="Maferax", vocab=vocab, width=z["width"], norm=dict(eps=1e-6), postln_alpha=3.0, logit_scale=0.25,
+    return dict(architecture="Maferax", vocab=vocab, width=z["width"], norm=dict(eps=1e-6), postln_alpha=2.0, logit_scale=0.5,
                 layers=layers)
 
 
