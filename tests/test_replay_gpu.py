@@ -171,6 +171,30 @@ def test_replay_of_a_fozedra_model(tmp_path, name, dtype):
     _replay_whole_tail_and_together(tmp_path, folder, V, reqs, exact, same, dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "M"])
+def test_replay_of_a_maferax_model(tmp_path, name, dtype):
+    """The fourth architecture through the same program, on the same schedule (in bfloat16 the whole prompts take the
+    expanded form of the latent attention and the single tokens its tensor-core form)."""
+    import plain_maferax
+    import tiny_maferax
+
+    folder = tiny_maferax.make_folder(tmp_path, name, seed=6)
+    cfg, tensors = tiny_maferax.load_plain(folder)
+    V = cfg["vocab"]
+    reqs = {k: tiny_maferax.prompt(n, V, seed=ord(k)) for k, n in {"a": 1, "b": 70, "c": 135, "d": 90}.items()}
+    exact, same = {}, {}
+    for k, t in reqs.items():
+        if dtype == "bfloat16":
+            # the exact model follows the experts that the rounded one chose: a close call is no error of the program
+            ids = {}
+            same[k] = plain_maferax.forward(t, tensors, cfg, rd=plain_maferax.to_bf16, ids_out=ids)[0]
+            exact[k] = plain_maferax.forward(t, tensors, cfg, expert_ids=ids)[0]
+        else:
+            exact[k] = same[k] = plain_maferax.forward(t, tensors, cfg)[0]
+    _replay_whole_tail_and_together(tmp_path, folder, V, reqs, exact, same, dtype)
+
+
 def _replay_whole_tail_and_together(tmp_path, folder, V, reqs, exact, same, dtype):
     """Requests a (1 token), b (70), c (135), d (90): c whole; d with its last 30 tokens one by one; a, b and c started
     together and decoded together until each has ended."""
