@@ -319,7 +319,7 @@ attn_prefill_simt_kernel(T* __restrict__ ctx, long long ldc, const T* __restrict
                          const int* __restrict__ seq_start, int QH, int KVH, int HD, int window,
                          float scale, const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot,
                          const T* __restrict__ pool, long long pages, const int* __restrict__ ptab,
-                         int ptab_stride, int ring, const float* __restrict__ sink) {
+                         int ptab_stride, int ring, const float* __restrict__ sink, float cap) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -389,7 +389,7 @@ attn_prefill_simt_kernel(T* __restrict__ ctx, long long ldc, const T* __restrict
             const float* kr = Ks + lane * ldq;
             float s = 0.f;
             for (int d = 0; d < HD; ++d) s = fmaf(qr[d], kr[d], s);
-            s *= scale;
+            s = soft_cap(s * scale, cap);
             const bool vis = qi < nq && kpos <= qpos && kpos < len && (window <= 0 || kpos + window > qpos);
             s = vis ? s : -INFINITY;
             const float mx = fmaxf(m[i], warp_max(s));
@@ -437,13 +437,14 @@ template <typename T, bool PAST>
 static int launch_attn_simt(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
                             const void* gate, long long ldg, const int* seq_start, int B, int max_len, int QH, int KVH,
                             int HD, int window, float scale, const int* seq_pos0, const int* seq_slot, const void* pool,
-                            long long pages, const int* ptab, int ptab_stride, int ring, const float* sink, cudaStream_t st) {
+                            long long pages, const int* ptab, int ptab_stride, int ring, const float* sink, float cap,
+                            cudaStream_t st) {
     const size_t smem = ((size_t)(AP_BQ + AP_BK) * (HD + 1) + (size_t)AP_BK * HD + AP_BQ * (AP_BK + 1)) * sizeof(float);
     dim3 grid((max_len + AP_BQ - 1) / AP_BQ, QH, B);
     cudaFuncSetAttribute(attn_prefill_simt_kernel<T, PAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cm_launch(attn_prefill_simt_kernel<T, PAST>, grid, 128, smem, st, (T*)ctx, ldc, (const T*)q, (const T*)k, (const T*)v,
               ld, (const T*)gate, ldg, seq_start, QH, KVH, HD, window, scale, seq_pos0, seq_slot, (const T*)pool, pages,
-              ptab, ptab_stride, ring, sink);
+              ptab, ptab_stride, ring, sink, cap);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
@@ -451,16 +452,16 @@ static int launch_attn_simt(void* ctx, long long ldc, const void* q, const void*
 extern "C" int cm_attn_prefill_simt(int dt, void* ctx, long long ldc, const void* q, const void* k,
                                     const void* v, long long ld, const void* gate, long long ldg,
                                     const int* seq_start, int B, int max_len, int QH, int KVH, int HD,
-                                    int window, float scale, const float* sink, cudaStream_t st) {
+                                    int window, float scale, float softcap, const float* sink, cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return CM_OK;
     if (HD > 32 * AP_MAXJ) CM_REFUSE("attn_prefill: head size %d above %d", HD, 32 * AP_MAXJ);
     if (QH % KVH) CM_REFUSE("attn_prefill: %d query heads over %d key heads", QH, KVH);
     if (dt == DT_F32)
         return launch_attn_simt<float, false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window,
-                                              scale, nullptr, nullptr, nullptr, 0, nullptr, 0, 0, sink, st);
+                                              scale, nullptr, nullptr, nullptr, 0, nullptr, 0, 0, sink, softcap, st);
     if (dt == DT_BF16)
         return launch_attn_simt<bf16, false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window,
-                                             scale, nullptr, nullptr, nullptr, 0, nullptr, 0, 0, sink, st);
+                                             scale, nullptr, nullptr, nullptr, 0, nullptr, 0, 0, sink, softcap, st);
     return CM_ERR_DTYPE;
 }
 
@@ -471,8 +472,8 @@ extern "C" int cm_attn_append_simt(int dt, void* ctx, long long ldc, const void*
                                    const void* v, long long ld, const void* gate, long long ldg,
                                    const int* seq_start, const int* seq_pos0, const int* seq_slot, const void* pool,
                                    long long pages, const int* ptab, long long ptab_stride, int ring, int B,
-                                   int max_len, int QH, int KVH, int HD, int window, float scale, const float* sink,
-                                   cudaStream_t st) {
+                                   int max_len, int QH, int KVH, int HD, int window, float scale, float softcap,
+                                   const float* sink, cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return CM_OK;
     if (HD > 32 * AP_MAXJ) CM_REFUSE("attn_append: head size %d above %d", HD, 32 * AP_MAXJ);
     if (QH % KVH) CM_REFUSE("attn_append: %d query heads over %d key heads", QH, KVH);
@@ -480,10 +481,10 @@ extern "C" int cm_attn_append_simt(int dt, void* ctx, long long ldc, const void*
     if (!seq_pos0 || !seq_slot || !pool || !ptab) CM_REFUSE("attn_append: positions, slots, cache and page table are needed");
     if (dt == DT_F32)
         return launch_attn_simt<float, true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window,
-                                             scale, seq_pos0, seq_slot, pool, pages, ptab, (int)ptab_stride, ring, sink, st);
+                                             scale, seq_pos0, seq_slot, pool, pages, ptab, (int)ptab_stride, ring, sink, softcap, st);
     if (dt == DT_BF16)
         return launch_attn_simt<bf16, true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window,
-                                            scale, seq_pos0, seq_slot, pool, pages, ptab, (int)ptab_stride, ring, sink, st);
+                                            scale, seq_pos0, seq_slot, pool, pages, ptab, (int)ptab_stride, ring, sink, softcap, st);
     return CM_ERR_DTYPE;
 }
 
@@ -550,7 +551,7 @@ attn_decode_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, cons
                    long long ldq, const int* __restrict__ seq_pos, const int* __restrict__ seq_slot,
                    const T* __restrict__ pool, long long pages, const int* __restrict__ ptab,
                    int ptab_stride, int ring, int window, int QH, int KVH, int HD, int n_chunks,
-                   float scale) {
+                   float scale, float cap) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -632,7 +633,7 @@ attn_decode_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, cons
                             for (int i = 0; i < 8; ++i) sg = fmaf(qr[g][i], kv8[u][i], sg);
                         }
                         for (int o = tpr >> 1; o > 0; o >>= 1) sg += __shfl_xor_sync(0xffffffffu, sg, o);
-                        if (dq == 0) ss[g * AD_CHUNK + warp * PAGE_TOKENS + row] = v_u ? sg * scale : -INFINITY;
+                        if (dq == 0) ss[g * AD_CHUNK + warp * PAGE_TOKENS + row] = v_u ? soft_cap(sg * scale, cap) : -INFINITY;
                     }
                 }
             }
@@ -670,7 +671,7 @@ attn_decode_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, cons
             }
 #pragma unroll
             for (int g = 0; g < AD_GB; ++g)
-                ss[g * AD_CHUNK + warp * PAGE_TOKENS + row] = vis ? s[g] * scale : -INFINITY;
+                ss[g * AD_CHUNK + warp * PAGE_TOKENS + row] = vis ? soft_cap(s[g] * scale, cap) : -INFINITY;
         }
         }
         __syncthreads();
@@ -790,7 +791,7 @@ __global__ void attn_decode_merge_kernel(T* __restrict__ ctx, long long ldc,
 int cm_attn_decode_mma_stage(float* part_o, float* part_ml, const void* q, long long ldq, const int* seq_pos,
                              const int* seq_slot, const void* pool, long long pages, const int* ptab,
                              int ptab_stride, int ring, int window, int B, int QH, int KVH, int HD, int n_chunks,
-                             float scale, int* n_parts_out, cudaStream_t st);
+                             float scale, float softcap, int* n_parts_out, cudaStream_t st);
 
 // Scratch: part_o holds B*QH*n_chunks*HD floats, part_ml B*QH*n_chunks*2 floats.
 // bfloat16 with a head size that is a multiple of 16 up to 128 runs its first stage on the
@@ -803,7 +804,7 @@ extern "C" int cm_attn_decode(int dt, void* ctx, long long ldc, const void* q, l
                               const void* gate, long long ldg, const int* seq_pos, const int* seq_slot,
                               const void* pool, long long pages, const int* ptab, int ptab_stride,
                               int ring, int window, int B, int QH, int KVH, int HD, int n_chunks,
-                              float scale, float* part_o, float* part_ml, const float* sink, cudaStream_t st) {
+                              float scale, float softcap, float* part_o, float* part_ml, const float* sink, cudaStream_t st) {
     if (B <= 0) return CM_OK;
     if (HD % 8 || HD < 8 || HD > CM_MAX_HEAD_DIM)
         CM_REFUSE("attn_decode: head size %d (multiples of 8 up to %d)", HD, CM_MAX_HEAD_DIM);
@@ -821,7 +822,7 @@ extern "C" int cm_attn_decode(int dt, void* ctx, long long ldc, const void* q, l
     do {                                                                                                           \
         cudaFuncSetAttribute(attn_decode_kernel<TT, GB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         cm_launch(attn_decode_kernel<TT, GB>, grid, AD_THREADS, smem, st, part_o, part_ml, (const TT*)q, ldq, seq_pos, \
-                  seq_slot, (const TT*)pool, pages, ptab, ptab_stride, ring, window, QH, KVH, HD, n_chunks, scale); \
+                  seq_slot, (const TT*)pool, pages, ptab, ptab_stride, ring, window, QH, KVH, HD, n_chunks, scale, softcap); \
     } while (0)
 #define AD_DISPATCH(TT)                   \
     do {                                  \
@@ -834,7 +835,7 @@ extern "C" int cm_attn_decode(int dt, void* ctx, long long ldc, const void* q, l
         ((uintptr_t)q & 3) == 0 && ((uintptr_t)pool & 15) == 0) {
         int n_parts = n_chunks;                    // blocks per (sequence, kv head): at most n_chunks
         const int rc = cm_attn_decode_mma_stage(part_o, part_ml, q, ldq, seq_pos, seq_slot, pool, pages, ptab,
-                                                ptab_stride, ring, window, B, QH, KVH, HD, n_chunks, scale,
+                                                ptab_stride, ring, window, B, QH, KVH, HD, n_chunks, scale, softcap,
                                                 &n_parts, st);
         if (rc != CM_OK) return rc;
         cm_launch(attn_decode_merge_kernel<bf16>, mgrid, mthreads, 0, st, (bf16*)ctx, ldc, part_o, part_ml,
@@ -913,5 +914,5 @@ extern "C" int cm_attn_decode_noalloc(int dt, void* ctx, long long ldc, const vo
     if (rc != CM_OK) return rc;
     // part_o first (16-byte aligned for any size since HD is a multiple of 8), then part_ml
     return cm_attn_decode(dt, ctx, ldc, q, ldq, gate, ldg, seq_pos, seq_slot, pool, pages, ptab, ptab_stride, ring,
-                          window, B, QH, KVH, HD, n_chunks, scale, scratch, scratch + o_floats, nullptr, st);
+                          window, B, QH, KVH, HD, n_chunks, scale, 0.f, scratch, scratch + o_floats, nullptr, st);
 }

@@ -63,7 +63,9 @@ attn_prefill_mma_kernel(bf16* __restrict__ ctx, long long ldc, const bf16* __res
                         const bf16* __restrict__ gate, long long ldg, const int* __restrict__ seq_start, int QH,
                         int KVH, int window, float scale_log2, const int* __restrict__ seq_pos0,
                         const int* __restrict__ seq_slot, const bf16* __restrict__ pool, long long pages,
-                        const int* __restrict__ ptab, int ptab_stride, int ring, const float* __restrict__ sink) {
+                        const int* __restrict__ ptab, int ptab_stride, int ring, const float* __restrict__ sink,
+                        float cap_in) {
+    // cap_in > 0: the scores are bounded, s <- cap tanh(s scale / cap); cap_in = scale / cap, and scale_log2 is then cap log2 e
     constexpr int LDS = HD + 8;                   // padded row, elements
     constexpr int CH = HD / 8;                    // 16-byte chunks per row
     extern __shared__ __align__(16) uint8_t fa_smem[];
@@ -189,6 +191,12 @@ attn_prefill_mma_kernel(bf16* __restrict__ ctx, long long ldc, const bf16* __res
                 mma16816(s[2 * jp + 1], qf[kk], kb[2], kb[3]);
             }
         }
+        if (cap_in > 0.f) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s[j][i] = tanh_fast(s[j][i] * cap_in);
+        }
         // ---- mask, running maximum
         const bool edge = key0 + FA_BK - 1 > q0 + warp * 16 || key0 + FA_BK > len ||
                           (window > 0 && key0 + window <= q0 + warp * 16 + 15);
@@ -285,6 +293,7 @@ struct FaPast {                      // where the keys and values below a sequen
     int ptab_stride;
     int ring;
     const float* sink;               // per query head, or null: a logit without key and value in the softmax's denominator
+    float softcap;                   // > 0: scores bounded to (-softcap, softcap) by a tanh
 };
 
 template <int HD, int BQ, bool PAST>
@@ -303,8 +312,10 @@ static int launch_fa_bq(void* ctx, long long ldc, const void* q, const void* k, 
     }
     dim3 grid((max_len + BQ - 1) / BQ, QH, B);
     cm_launch(kernel, grid, BQ * 2, smem, st, (bf16*)ctx, ldc, (const bf16*)q, (const bf16*)k, (const bf16*)v, ld,
-              (const bf16*)gate, ldg, seq_start, QH, KVH, window, scale * 1.4426950408889634f, past.seq_pos0,
-              past.seq_slot, (const bf16*)past.pool, past.pages, past.ptab, past.ptab_stride, past.ring, past.sink);
+              (const bf16*)gate, ldg, seq_start, QH, KVH, window,
+              (past.softcap > 0.f ? past.softcap : scale) * 1.4426950408889634f, past.seq_pos0,
+              past.seq_slot, (const bf16*)past.pool, past.pages, past.ptab, past.ptab_stride, past.ring, past.sink,
+              past.softcap > 0.f ? scale / past.softcap : 0.f);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
@@ -345,10 +356,10 @@ static int dispatch_fa(void* ctx, long long ldc, const void* q, const void* k, c
 // buffer with a row pitch that is a multiple of 8 elements and 16-byte aligned bases.
 extern "C" int cm_attn_prefill_mma(void* ctx, long long ldc, const void* q, const void* k, const void* v,
                                    long long ld, const void* gate, long long ldg, const int* seq_start, int B,
-                                   int max_len, int QH, int KVH, int HD, int window, float scale, const float* sink,
-                                   cudaStream_t st) {
+                                   int max_len, int QH, int KVH, int HD, int window, float scale, float softcap,
+                                   const float* sink, cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return CM_OK;
-    const FaPast none = {nullptr, nullptr, nullptr, 0, nullptr, 0, 0, sink};
+    const FaPast none = {nullptr, nullptr, nullptr, 0, nullptr, 0, 0, sink, softcap};
     return dispatch_fa<false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window, scale, none, st);
 }
 
@@ -358,12 +369,12 @@ extern "C" int cm_attn_append_mma(void* ctx, long long ldc, const void* q, const
                                   long long ld, const void* gate, long long ldg, const int* seq_start,
                                   const int* seq_pos0, const int* seq_slot, const void* pool, long long pages,
                                   const int* ptab, long long ptab_stride, int ring, int B, int max_len, int QH, int KVH,
-                                  int HD, int window, float scale, const float* sink, cudaStream_t st) {
+                                  int HD, int window, float scale, float softcap, const float* sink, cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return CM_OK;
     if (ring % PAGE_TOKENS) CM_REFUSE("attn_append_mma: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
     if (!seq_pos0 || !seq_slot || !pool || !ptab)
         CM_REFUSE("attn_append_mma: positions, slots, cache and page table are needed");
-    const FaPast past = {seq_pos0, seq_slot, pool, pages, ptab, (int)ptab_stride, ring, sink};
+    const FaPast past = {seq_pos0, seq_slot, pool, pages, ptab, (int)ptab_stride, ring, sink, softcap};
     return dispatch_fa<true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window, scale, past, st);
 }
 
@@ -393,7 +404,7 @@ __global__ void __launch_bounds__(128)
 attn_decode_mma_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
                        long long ldq, const int* __restrict__ seq_pos, const int* __restrict__ seq_slot,
                        const bf16* __restrict__ pool, long long pages, const int* __restrict__ ptab, int ptab_stride,
-                       int ring, int window, int QH, int KVH, int n_parts, float scale_log2) {
+                       int ring, int window, int QH, int KVH, int n_parts, float scale_log2, float cap_in) {
     constexpr int LDS = HD + 8;
     constexpr int CH = HD / 8;
     extern __shared__ __align__(16) uint8_t fd_smem[];
@@ -477,6 +488,12 @@ attn_decode_mma_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, 
             __syncwarp();                                      // every lane has read the keys
             if (next_live) request(Ks, 0, next_idx);
             cp_async_commit();
+            if (cap_in > 0.f) {                 // bounded scores: tanh(s scale / cap), and cap log2 e in the exponent
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) s[j][i] = tanh_fast(s[j][i] * cap_in);
+            }
             // visibility of the page's entries (columns of s); raw scores, the scale goes into the exponent
             if (mask_all || (page_idx + 1) * FD_PAGE > n_entries) {
 #pragma unroll
@@ -609,7 +626,7 @@ extern "C" void cm_attn_decode_set_target_blocks(int blocks) { g_fd_target_block
 template <int HD>
 static int launch_fd(float* part_o, float* part_ml, const void* q, long long ldq, const int* seq_pos,
                      const int* seq_slot, const void* pool, long long pages, const int* ptab, int ptab_stride,
-                     int ring, int window, int B, int QH, int KVH, int n_chunks, float scale, int* n_parts_out,
+                     int ring, int window, int B, int QH, int KVH, int n_chunks, float scale, float softcap, int* n_parts_out,
                      cudaStream_t st) {
     const size_t smem = (size_t)4 * 2 * FD_PAGE * (HD + 8) * sizeof(bf16);
     auto kernel = attn_decode_mma_kernel<HD>;
@@ -643,7 +660,7 @@ static int launch_fd(float* part_o, float* part_ml, const void* q, long long ldq
     *n_parts_out = n_parts;
     cm_launch(kernel, dim3(n_parts, KVH, B), 128, smem, st, part_o, part_ml, (const bf16*)q, ldq, seq_pos, seq_slot,
               (const bf16*)pool, pages, ptab, ptab_stride, ring, window, QH, KVH, n_parts,
-              scale * 1.4426950408889634f);
+              (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, softcap > 0.f ? scale / softcap : 0.f);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
@@ -654,11 +671,11 @@ static int launch_fd(float* part_o, float* part_ml, const void* q, long long ldq
 int cm_attn_decode_mma_stage(float* part_o, float* part_ml, const void* q, long long ldq, const int* seq_pos,
                              const int* seq_slot, const void* pool, long long pages, const int* ptab,
                              int ptab_stride, int ring, int window, int B, int QH, int KVH, int HD, int n_chunks,
-                             float scale, int* n_parts_out, cudaStream_t st) {
+                             float scale, float softcap, int* n_parts_out, cudaStream_t st) {
     if (ldq % 2 || ((uintptr_t)q & 3) || ((uintptr_t)pool & 15)) CM_REFUSE("attn_decode_mma: misaligned operands");
 #define FD_CASE(D) \
     case D: return launch_fd<D>(part_o, part_ml, q, ldq, seq_pos, seq_slot, pool, pages, ptab, ptab_stride, ring, \
-                                window, B, QH, KVH, n_chunks, scale, n_parts_out, st);
+                                window, B, QH, KVH, n_chunks, scale, softcap, n_parts_out, st);
     switch (HD) {
         FD_CASE(16) FD_CASE(32) FD_CASE(48) FD_CASE(64) FD_CASE(80) FD_CASE(96) FD_CASE(112) FD_CASE(128)
         default: CM_REFUSE("attn_decode_mma: head size %d (multiples of 16 up to 128)", HD);

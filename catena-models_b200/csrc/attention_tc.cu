@@ -164,6 +164,8 @@ struct FtPast {                      // where the keys and values below a sequen
     long long pages;
     int ring;
     const float* sink;               // per query head, or null: a logit without key and value in the softmax's denominator
+    float softcap;                   // > 0: scores bounded to (-softcap, softcap) by a tanh, and
+    float cap_in;                    // scale / softcap, what a raw score is multiplied by inside the tanh (0: no bound)
 };
 
 // One work item: a 128-query tile of one query head of one sequence, and the key tiles it takes.
@@ -509,6 +511,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (T >= 2 && products_done == T - 2)
                     early = ft_mbar_test(o_full + 8 * (g * NP + (T - 2) % NP), (uint32_t)(((T - 2) / NP) & 1));
                 tmem_load_wait();
+                if (past.cap_in > 0.f) {                             // bounded scores: tanh(s scale / cap); cap log2 e is in scale_log2
+#pragma unroll
+                    for (int c = 0; c < FT_TILE; ++c) v[c] = tanh_fast(v[c] * past.cap_in);
+                }
                 // the keys of the tile that this row sees are the columns lo .. hi - 1; all of them: no comparisons needed
                 const int lo = window > 0 ? max(0, row - window + 1 - k0) : 0;
                 const int hi = min(FT_TILE, min(row, limit - 1) - k0 + 1);
@@ -735,7 +741,7 @@ static int launch_ft(void* ctx, long long ldc, const void* q, const void* k, con
     const long long blocks = SOLO ? (items + 1) / 2 : items;
     dim3 grid((unsigned)(blocks < sm_count ? blocks : sm_count));
     cm_launch(kernel, grid, FT_THREADS, smem, st, map_q, map_k, map_v, map_pool, past, (bf16*)ctx, ldc, (const bf16*)gate,
-              ldg, seq_start, QH, KVH, B, tiles_x, window, scale * 1.4426950408889634f, err);
+              ldg, seq_start, QH, KVH, B, tiles_x, window, (past.softcap > 0.f ? past.softcap : scale) * 1.4426950408889634f, err);
     {
         cudaError_t e_ = cudaGetLastError();
         if (e_ != cudaSuccess) {
@@ -754,13 +760,13 @@ static int launch_ft(void* ctx, long long ldc, const void* q, const void* k, con
 // base and pitch.  err: device int that a block raises when one of its bounded waits runs out.
 extern "C" int cm_attn_prefill_tc(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
                                   const void* gate, long long ldg, const int* seq_start, int B, int max_len,
-                                  long long T, int QH, int KVH, int HD, int window, float scale, const float* sink,
-                                  int* err, cudaStream_t st) {
+                                  long long T, int QH, int KVH, int HD, int window, float scale, float softcap,
+                                  const float* sink, int* err, cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return CM_OK;
     if (QH % KVH) CM_REFUSE("attn_prefill_tc: %d query heads over %d key heads", QH, KVH);
     if (ld % 8 || ldc % 8 || (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)ctx) & 15))
         CM_REFUSE("attn_prefill_tc: row pitches %lld, %lld must be multiples of 8 and the operands 16-byte aligned", ld, ldc);
-    const FtPast none = {nullptr, nullptr, nullptr, 0, 0, 0, sink};
+    const FtPast none = {nullptr, nullptr, nullptr, 0, 0, 0, sink, softcap, softcap > 0.f ? scale / softcap : 0.f};
     if (HD == 64)
         return launch_ft<64, FT_STAGES_64, false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
                                        none, nullptr, err, st);
@@ -778,7 +784,7 @@ extern "C" int cm_attn_append_tc(void* ctx, long long ldc, const void* q, const 
                                  const void* gate, long long ldg, const int* seq_start, const int* seq_pos0,
                                  const int* seq_slot, const void* pool, long long pages, const int* ptab,
                                  long long ptab_stride, int ring, int B, int max_len, long long T, int QH, int KVH,
-                                 int HD, int window, float scale, const float* sink, int* err, cudaStream_t st) {
+                                 int HD, int window, float scale, float softcap, const float* sink, int* err, cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return CM_OK;
     if (QH % KVH) CM_REFUSE("attn_append_tc: %d query heads over %d key heads", QH, KVH);
     if (ring % PAGE_TOKENS) CM_REFUSE("attn_append_tc: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
@@ -787,7 +793,7 @@ extern "C" int cm_attn_append_tc(void* ctx, long long ldc, const void* q, const 
     if (ld % 8 || ldc % 8 || (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)ctx | (uintptr_t)pool) & 15))
         CM_REFUSE("attn_append_tc: row pitches %lld, %lld must be multiples of 8 and the operands 16-byte aligned", ld, ldc);
     if (2 * pages * KVH * PAGE_TOKENS > 0x7fffffffLL) CM_REFUSE("attn_append_tc: a cache of %lld pages is too large", pages);
-    const FtPast past = {seq_pos0, seq_slot, ptab, ptab_stride, pages, ring, sink};
+    const FtPast past = {seq_pos0, seq_slot, ptab, ptab_stride, pages, ring, sink, softcap, softcap > 0.f ? scale / softcap : 0.f};
     if (HD == 64)
         return launch_ft<64, FT_STAGES_64, true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
                                       past, pool, err, st);

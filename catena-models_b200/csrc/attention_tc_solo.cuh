@@ -277,6 +277,10 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(s_read);
+                if (past.cap_in > 0.f) {                             // bounded scores: tanh(s scale / cap); cap log2 e is in scale_log2
+#pragma unroll
+                    for (int c = 0; c < FT_TILE; ++c) v[c] = tanh_fast(v[c] * past.cap_in);
+                }
                 // the keys of the tile that this row sees are the columns lo .. hi - 1; all of them: no comparisons needed
                 const int lo = window > 0 ? max(0, row - window + 1 - k0) : 0;
                 const int hi = min(FT_TILE, min(row, limit - 1) - k0 + 1);

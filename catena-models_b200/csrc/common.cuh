@@ -154,7 +154,31 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return t;
 }
 
+// A score bounded to (-cap, cap): cap * tanh(s / cap); cap <= 0 leaves it as it is.
+__device__ __forceinline__ float soft_cap(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+// tanh from one exponential and one division (absolute error of a few 2^-24: for kernels that form
+// thousands of them per row and round what follows to bfloat16).
+__device__ __forceinline__ float tanh_fast(float x) {
+    const float t = __expf(2.f * fminf(fmaxf(x, -15.f), 15.f));
+    return 1.f - __fdividef(2.f, t + 1.f);
+}
 __device__ __forceinline__ float sigmoid_f32(float x) { return 1.f / (1.f + expf(-x)); }
+
+// What a gated feed-forward makes of its gate half g and its up half u.
+//   act 0: silu(g) u;   act 1: the tanh form of gelu on g, times u;
+//   act 2: both halves clamped first, g' = min(g, limit), u' = clamp(u, -limit, limit): g' sigmoid(1.702 g') (u' + 1)
+#define CM_ACT_SILU 0
+#define CM_ACT_GELU_TANH 1
+#define CM_ACT_CLAMPED_SWISH 2
+__device__ __forceinline__ float gated_act(float g, float u, int act, float limit) {
+    if (act == CM_ACT_CLAMPED_SWISH) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g * sigmoid_f32(1.702f * g) * (u + 1.f);
+    }
+    if (act == CM_ACT_GELU_TANH) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    return g * sigmoid_f32(g) * u;
+}
 
 // Eight consecutive elements as floats: one 16-byte access for bfloat16, two for float.
 template <typename T>

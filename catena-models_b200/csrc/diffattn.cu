@@ -38,6 +38,13 @@ struct TapRotArgs {
     const int *tok_seq, *tok_pos, *seq_start, *seq_pos0, *seq_slot;
     int T, B, QC, KC, VC, K, sub, rot, G, KW, DV, HDC;
     int one_token_each;          // every sequence brings one token on top of held ones: the state moves on in the same launch
+    // further forms, all off at 0
+    int interleaved;             // the rotation pairs channel 2i with 2i + 1 (rate[i]) instead of i with i + rot/2
+    int value_from_key;          // no value channels (VC = 0): a position's value row is its key row before the rotation
+    int ring;                    // > 0: the pages are a ring of this many entries; position p lies in entry p % ring, and of a
+                                 // step only the last `ring` positions of a sequence are written
+    int no_store;                // the cache is left as it is (the caller writes the step's rows later)
+    int rows_out;                // q_out rows hold [q | turned k | v] (ldq >= QC + KC + value channels), not the queries alone
 };
 
 #define TR_THREADS 128
@@ -83,7 +90,9 @@ tap_rotate_store_kernel(const TapRotArgs a) {
     const int half = a.rot >> 1;
     const int cr = c < a.QC ? c : c - a.QC;           // channel within q, or within k | v
     const int e = cr % max(a.sub, 1);
-    const bool turned = c < a.QC + a.KC && a.rate && e < a.rot, low = e < half;
+    const bool turned = c < a.QC + a.KC && a.rate && e < a.rot, low = a.interleaved ? !(e & 1) : e < half;
+    const int partner = a.interleaved ? (low ? c + 1 : c - 1) : (low ? c + half : c - half);
+    const int pair = a.interleaved ? e >> 1 : (low ? e : e - half);
     float y[TOK], other[TOK];
     int bs[TOK];
 #pragma unroll
@@ -95,7 +104,7 @@ tap_rotate_store_kernel(const TapRotArgs a) {
         const int pos = a.tok_pos[t], p0 = a.seq_pos0[bs[i]];
         const float* st = a.state + (long long)a.seq_slot[bs[i]] * a.state_stride;
         y[i] = tap_sum<T>(a, c, t, pos, p0, st);
-        if (turned) other[i] = tap_sum<T>(a, low ? c + half : c - half, t, pos, p0, st);
+        if (turned) other[i] = tap_sum<T>(a, partner, t, pos, p0, st);
     }
 #pragma unroll
     for (int i = 0; i < TOK; ++i) {
@@ -105,7 +114,7 @@ tap_rotate_store_kernel(const TapRotArgs a) {
         float v = y[i];
         if (turned) {
             float sn, cs;
-            sincosf((float)pos * a.rate[low ? e : e - half], &sn, &cs);
+            sincosf((float)pos * a.rate[pair], &sn, &cs);
             sn *= a.mag;
             cs *= a.mag;
             v = low ? v * cs - other[i] * sn : v * cs + other[i] * sn;
@@ -113,13 +122,34 @@ tap_rotate_store_kernel(const TapRotArgs a) {
         if (c < a.QC) {
             ((T*)a.q_out)[(long long)t * a.ldq + c] = from_f32<T>(v);
         } else {
-            const int page = a.ptab[(long long)a.seq_slot[b] * a.ptab_stride + pos / PAGE_TOKENS], row = pos % PAGE_TOKENS;
-            if (cr < a.KC) {
-                const int g = cr / a.KW, off = cr - g * a.KW;
-                kv_tile((T*)a.pool, 0, a.pages, page, g, a.G, a.HDC)[(long long)row * a.HDC + off] = from_f32<T>(v);
-            } else {
-                const int cv = cr - a.KC, g = cv / a.DV, off = cv - g * a.DV;
-                kv_tile((T*)a.pool, 1, a.pages, page, g, a.G, a.HDC)[(long long)row * a.HDC + off] = from_f32<T>(v);
+            if (a.rows_out) {
+                // the step's rows side by side: turned keys behind the queries, values behind the keys
+                T* o = (T*)a.q_out + (long long)t * a.ldq + a.QC;
+                if (cr < a.KC) {
+                    o[cr] = from_f32<T>(v);
+                    if (a.value_from_key) o[a.KC + cr] = from_f32<T>(y[i]);
+                } else {
+                    o[cr] = from_f32<T>(v);
+                }
+            }
+            bool keep = !a.no_store;
+            int entry = pos;
+            if (a.ring > 0) {
+                const int end = a.seq_pos0[b] + a.seq_start[b + 1] - a.seq_start[b];
+                keep = keep && pos >= end - a.ring;
+                entry = pos % a.ring;
+            }
+            if (keep) {
+                const int page = a.ptab[(long long)a.seq_slot[b] * a.ptab_stride + entry / PAGE_TOKENS], row = entry % PAGE_TOKENS;
+                if (cr < a.KC) {
+                    const int g = cr / a.KW, off = cr - g * a.KW;
+                    kv_tile((T*)a.pool, 0, a.pages, page, g, a.G, a.HDC)[(long long)row * a.HDC + off] = from_f32<T>(v);
+                    if (a.value_from_key)
+                        kv_tile((T*)a.pool, 1, a.pages, page, g, a.G, a.HDC)[(long long)row * a.HDC + off] = from_f32<T>(y[i]);
+                } else {
+                    const int cv = cr - a.KC, g = cv / a.DV, off = cv - g * a.DV;
+                    kv_tile((T*)a.pool, 1, a.pages, page, g, a.G, a.HDC)[(long long)row * a.HDC + off] = from_f32<T>(v);
+                }
             }
         }
         if (a.one_token_each && a.K > 1) {
@@ -159,7 +189,10 @@ extern "C" int cm_tap_rotate_store(int dt, const TapRotArgs* args, cudaStream_t 
         CM_REFUSE("tap_rotate_store: %d turned channels in vectors of %d", a.rot, a.sub);
     if ((a.KC || a.VC) && (!a.pool || a.KW > a.HDC || a.DV > a.HDC || a.KC != a.G * a.KW || a.VC != a.G * a.DV))
         CM_REFUSE("tap_rotate_store: %d key and %d value channels do not fit %d heads of %d", a.KC, a.VC, a.G, a.HDC);
-    if (a.K > 1 && a.state_stride < (long long)a.K * C) CM_REFUSE("tap_rotate_store: a state row of %lld floats is too short", a.state_stride);
+    if (a.K > 1 && (!a.state || a.state_stride < (long long)a.K * C)) CM_REFUSE("tap_rotate_store: a state row of %lld floats is too short", a.state_stride);
+    if (a.value_from_key && a.VC) CM_REFUSE("tap_rotate_store: values that are the keys come without value channels");
+    if (a.interleaved && a.rate && a.rot % 2) CM_REFUSE("tap_rotate_store: %d turned channels in pairs", a.rot);
+    if (a.ring < 0 || a.ring % PAGE_TOKENS) CM_REFUSE("tap_rotate_store: a ring of %d entries (whole pages)", a.ring);
     const bool many = a.T >= 512 && !a.one_token_each;               // long steps: four tokens a thread
     dim3 grid(many ? (a.T + 3) / 4 : a.T, (C + TR_THREADS - 1) / TR_THREADS), sgrid((C + TR_THREADS - 1) / TR_THREADS, a.B);
     if (dt == DT_F32) {

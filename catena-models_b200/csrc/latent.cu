@@ -28,7 +28,7 @@ latent_prepare_kernel(const LatentArgs a) {
     pdl_wait();
     const long long t = blockIdx.x;
     const int b = a.tok_seq[t];
-    T* copy = a.ckv ? (T*)a.ckv + t * a.EC : nullptr;
+    T* copy = a.ckv && !a.no_entry ? (T*)a.ckv + t * a.EC : nullptr;
     if (b < 0) {
         if (copy)
             for (int c = threadIdx.x; c < a.EC; c += blockDim.x) copy[c] = from_f32<T>(0.f);
@@ -48,6 +48,7 @@ latent_prepare_kernel(const LatentArgs a) {
         T* o = (T*)a.cq + t * a.QR;
         for (int c = threadIdx.x; c < a.QR; c += blockDim.x) o[c] = from_f32<T>((to_f32(x[c]) * inv) * a.wq_norm[c]);
     }
+    if (a.no_entry) return;
     // the cache entry
     const int pos = a.tok_pos[t];
     const int page = a.ptab[(long long)a.seq_slot[b] * a.ptab_stride + pos / PAGE_TOKENS];
@@ -69,6 +70,8 @@ latent_prepare_kernel(const LatentArgs a) {
         }
         float sn, cs;
         sincosf((float)pos * a.rate[i], &sn, &cs);
+        sn *= a.mag;
+        cs *= a.mag;
         const float u = to_f32(r[2 * i]), v = to_f32(r[2 * i + 1]);
         entry[a.KR + 2 * i] = from_f32<T>(u * cs - v * sn);
         entry[a.KR + 2 * i + 1] = from_f32<T>(v * cs + u * sn);
@@ -99,7 +102,11 @@ latent_expand_kernel(const LatentArgs a) {
     const T* kvu = (const T*)a.kvu + t * a.ld_kvu;
     const T* r = (const T*)a.ckv + t * a.EC + a.KR;
     const float pos = pad ? 0.f : (float)a.tok_pos[t];
-    for (int i = threadIdx.x; i < R / 2; i += blockDim.x) sincosf(pos * a.rate[i], &sn_tab[i], &cs_tab[i]);
+    for (int i = threadIdx.x; i < R / 2; i += blockDim.x) {
+        sincosf(pos * a.rate[i], &sn_tab[i], &cs_tab[i]);
+        sn_tab[i] *= a.mag;
+        cs_tab[i] *= a.mag;
+    }
     __syncthreads();
     const int n = H * HD;
     if (VEC) {
@@ -189,6 +196,8 @@ __global__ void latent_query_turn_kernel(const LatentArgs a) {
     }
     float sn, cs;
     sincosf((float)a.tok_pos[t] * a.rate[i], &sn, &cs);
+    sn *= a.mag;
+    cs *= a.mag;
     const float u = to_f32(q[2 * i]), v = to_f32(q[2 * i + 1]);
     o[2 * i] = u * cs - v * sn;
     o[2 * i + 1] = v * cs + u * sn;

@@ -10,7 +10,7 @@ struct LatentArgs {
     int q_off, kv_off;           // columns where the two begin
     void* cq;                    // [rows][QR]: the normed query latent, for the product that makes the heads' queries
     const float *wq_norm, *wkv_norm;   // [QR], [KR]
-    const float* rate;           // [R / 2]: angle of pair i = position * rate[i] (0: the pair stays)
+    const float* rate;           // [R / 2]: angle of pair i = position * rate[i] (0: the pair stays; times `mag` below)
     void* q;                     // [rows][H][D + R] the heads' queries as the product left them
     long long ldq;
     float* qa;                   // [rows][H][E], E = KR + R: per head the query against the latent, then its turned part
@@ -38,6 +38,8 @@ struct LatentArgs {
     void* qkv;                   // [rows][ld_qkv]: queries, keys and values in heads of HD channels, zeros behind each head
     long long ld_qkv;
     int HD, DV;
+    float mag;                   // the factor on every sine and cosine (1: a plain rotation)
+    int no_entry;                // latent_prepare: the layer reads another layer's entries; only the query latent is made
 };
 
 // The splits' (maximum, sum, sums over the latents) of every (row, head) merged, normalised and gated (latent.cu); both

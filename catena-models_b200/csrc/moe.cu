@@ -32,8 +32,9 @@ struct RouteRule {
     float renorm_eps;
     float scale;               // factor on the weights
     const float* correction;   // null, or [E]: added to the scores for the choice only; the weights are the scores themselves
-    int groups, keep;          // groups > 0: the experts form `groups` equal groups of neighbours, a group's score is its largest
-                               // choice score, and only experts of the best `keep` groups can be chosen
+    int groups, keep;          // groups > 0: the experts form `groups` equal groups of neighbours, a group's score is the sum of
+    int group_best;            // its `group_best` largest choice scores (1: its largest), and only experts of the best `keep`
+                               // groups can be chosen
     int real;                  // experts real .. E-1 are identity experts: they get a weight but no rows (their output is the input)
 };
 
@@ -55,9 +56,28 @@ __device__ void choose_experts(float* sc, float* ch, int E, int top, const Route
         // equal one and a lower index); a closed group's choice scores count as minus infinity
         const int n = E / r.groups;
         float best[MOE_MAX_GROUPS];
+        const int nb = min(max(r.group_best, 1), n);
         for (int g = 0; g < r.groups; ++g) {
-            best[g] = -INFINITY;
-            for (int e = g * n; e < (g + 1) * n; ++e) best[g] = fmaxf(best[g], ch[e]);
+            if (nb == 1) {
+                best[g] = -INFINITY;
+                for (int e = g * n; e < (g + 1) * n; ++e) best[g] = fmaxf(best[g], ch[e]);
+                continue;
+            }
+            // the sum of the nb largest: each pass takes the largest not yet taken (the lower index among equals)
+            unsigned long long taken = 0ull;                    // n <= 64 experts a group
+            float sum = 0.f;
+            for (int j = 0; j < nb; ++j) {
+                int at = -1;
+                float bv = -INFINITY;
+                for (int e = 0; e < n; ++e)
+                    if (!((taken >> e) & 1ull) && (at < 0 || ch[g * n + e] > bv)) {
+                        bv = ch[g * n + e];
+                        at = e;
+                    }
+                taken |= 1ull << at;
+                sum += bv;
+            }
+            best[g] = sum;
         }
         for (int g = 0; g < r.groups; ++g) {
             int ahead = 0;
@@ -281,8 +301,10 @@ static int max_tiles_for(long long pairs, int E, int tile_rows) {
 extern "C" int cm_moe_route(int dt, int* ids, float* wts, int* perm, int* dest, int* work, const void* h, const void* wr,
                             const int* tok_seq, long long rows, int W, int E, int top, int softmax_gate,
                             int renormalize, int tile_rows, void* xs, int apply_weight, const float* correction, int groups,
-                            int keep, int identity, float scale, float renorm_eps, cudaStream_t st) {
+                            int keep, int identity, float scale, float renorm_eps, int group_best, cudaStream_t st) {
     if (rows <= 0) return CM_OK;
+    if (groups > 0 && (group_best < 1 || E / groups > 64 && group_best > 1))
+        CM_REFUSE("moe_route: the sum of the %d best of a group of %d experts", group_best, E / groups);
     if (top < 1 || top > E) CM_REFUSE("moe_route: %d of %d experts", top, E);
     if (identity < 0 || identity >= E) CM_REFUSE("moe_route: %d identity experts of %d", identity, E);
     if (groups < 0 || groups > MOE_MAX_GROUPS || (groups > 0 && (E % groups || keep < 1 || keep > groups || keep * (E / groups) < top)))
@@ -298,6 +320,7 @@ extern "C" int cm_moe_route(int dt, int* ids, float* wts, int* perm, int* dest, 
     rule.correction = correction;
     rule.groups = groups;
     rule.keep = keep;
+    rule.group_best = group_best;
     rule.real = E - identity;
     // the scratch is laid out for the experts that get rows (the Python side sizes it by their number)
     const int ER = rule.real;
@@ -377,7 +400,7 @@ template <typename T, bool UP>
 __global__ void __launch_bounds__(MOE_THREADS)
 moe_grouped_kernel(void* __restrict__ out, const T* __restrict__ x, const T* __restrict__ w,
                    const int* __restrict__ plan, const int* __restrict__ perm, const float* __restrict__ wts,
-                   int top, int N, int K, int apply_weight, int gelu) {
+                   int top, int N, int K, int apply_weight, int act, float limit) {
     __shared__ float xs[MOE_BK][MOE_TM + 1];
     __shared__ float ws[UP ? 2 : 1][MOE_BK][MOE_TN + 1];
     __shared__ int src_row[MOE_TM];
@@ -446,10 +469,7 @@ moe_grouped_kernel(void* __restrict__ out, const T* __restrict__ x, const T* __r
             if (n >= N) continue;
             if (UP) {
                 const float g = acc[0][i][c], u = acc[1][i][c];
-                float act;
-                if (gelu) act = 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
-                else act = g * sigmoid_f32(g);
-                reinterpret_cast<T*>(out)[(long long)(row0 + r) * N + n] = from_f32<T>(act * u);
+                reinterpret_cast<T*>(out)[(long long)(row0 + r) * N + n] = from_f32<T>(gated_act(g, u, act, limit));
             } else {
                 float y = acc[0][i][c];
                 if (apply_weight) y *= row_w[r];
@@ -461,16 +481,16 @@ moe_grouped_kernel(void* __restrict__ out, const T* __restrict__ x, const T* __r
 
 template <typename T>
 static int launch_grouped(bool up, void* out, const void* x, const void* w, const int* work, const int* perm,
-                          const float* wts, int E, int top, int max_tiles, int N, int K, int apply_weight, int gelu,
+                          const float* wts, int E, int top, int max_tiles, int N, int K, int apply_weight, int act, float limit,
                           cudaStream_t st) {
     const int* plan = work + 2 * E;
     dim3 grid(max_tiles, (N + MOE_TN - 1) / MOE_TN);
     if (up)
         cm_launch(moe_grouped_kernel<T, true>, grid, MOE_THREADS, 0, st, out, (const T*)x, (const T*)w, plan, perm, wts, top, N,
-                  K, apply_weight, gelu);
+                  K, apply_weight, act, limit);
     else
         cm_launch(moe_grouped_kernel<T, false>, grid, MOE_THREADS, 0, st, out, (const T*)x, (const T*)w, plan, perm, wts, top, N,
-                  K, apply_weight, gelu);
+                  K, apply_weight, act, limit);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
@@ -479,9 +499,9 @@ static int launch_grouped(bool up, void* out, const void* x, const void* w, cons
 // up == 0: the second product (N = the model's width, K = the inner width), rows of float by pair.
 extern "C" int cm_moe_grouped(int dt, int up, void* out, const void* x, const void* w, const int* work,
                               const int* perm, const float* wts, int E, int top, int max_tiles, int N, int K,
-                              int apply_weight, int gelu, cudaStream_t st) {
+                              int apply_weight, int act, float limit, cudaStream_t st) {
     if (max_tiles <= 0) return CM_OK;
-    if (dt == DT_F32) return launch_grouped<float>(up != 0, out, x, w, work, perm, wts, E, top, max_tiles, N, K, apply_weight, gelu, st);
-    if (dt == DT_BF16) return launch_grouped<bf16>(up != 0, out, x, w, work, perm, wts, E, top, max_tiles, N, K, apply_weight, gelu, st);
+    if (dt == DT_F32) return launch_grouped<float>(up != 0, out, x, w, work, perm, wts, E, top, max_tiles, N, K, apply_weight, act, limit, st);
+    if (dt == DT_BF16) return launch_grouped<bf16>(up != 0, out, x, w, work, perm, wts, E, top, max_tiles, N, K, apply_weight, act, limit, st);
     return CM_ERR_DTYPE;
 }

@@ -374,9 +374,10 @@ extern "C" int cm_add_norm(int dt, void* h_out, void* n_out, const void* m, cons
 
 // --------------------------------------------------------------------------- SwiGLU
 // a[t,f] = T(act(g) * u), g = gu[t, f], u = gu[t, F + f]  (gate | up packed rows); act 0: g * sigmoid(g),
-// act 1: the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+// act 1: the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))); act 2: both halves clamped at
+// `limit`, min(g, limit) sigmoid(1.702 min(g, limit)) (clamp(u) + 1)  (gated_act in common.cuh).
 template <typename T>
-__global__ void swiglu_kernel(T* __restrict__ a, const T* __restrict__ gu, long long total, int F, int act) {
+__global__ void swiglu_kernel(T* __restrict__ a, const T* __restrict__ gu, long long total, int F, int act, float limit) {
     pdl_trigger();
     pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -385,19 +386,18 @@ __global__ void swiglu_kernel(T* __restrict__ a, const T* __restrict__ gu, long 
     const int f = (int)(i - t * F);
     const float g = to_f32(gu[t * 2 * F + f]);
     const float u = to_f32(gu[t * 2 * F + F + f]);
-    const float ag = act == 1 ? 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g * sigmoid_f32(g);
-    a[i] = from_f32<T>(ag * u);
+    a[i] = from_f32<T>(gated_act(g, u, act, limit));
 }
 
-extern "C" int cm_swiglu(int dt, void* a, const void* gu, int rows, int F, int act, cudaStream_t st) {
+extern "C" int cm_swiglu(int dt, void* a, const void* gu, int rows, int F, int act, float limit, cudaStream_t st) {
     const long long total = (long long)rows * F;
     if (total <= 0) return CM_OK;
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (dt == DT_F32)
-        cm_launch(swiglu_kernel<float>, blocks, threads, 0, st, (float*)a, (const float*)gu, total, F, act);
+        cm_launch(swiglu_kernel<float>, blocks, threads, 0, st, (float*)a, (const float*)gu, total, F, act, limit);
     else if (dt == DT_BF16)
-        cm_launch(swiglu_kernel<bf16>, blocks, threads, 0, st, (bf16*)a, (const bf16*)gu, total, F, act);
+        cm_launch(swiglu_kernel<bf16>, blocks, threads, 0, st, (bf16*)a, (const bf16*)gu, total, F, act, limit);
     else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();

@@ -261,10 +261,16 @@ class Runtime:
         that kernel's fused forms, which take no more)."""
         return x.shape[0] <= self.SKINNY_BEST_ROWS and self._product_kernel(x, w) == "skinny"
 
-    def gate_up_swiglu(self, x, w_gate_up, F, gelu=False):
+    def gate_up_swiglu(self, x, w_gate_up, F, gelu=False, limit=None):
         """a = act(x Wgate^T) * (x Wup^T) for the row-packed [Wgate; Wup]; act is silu, or with `gelu` the tanh form of
-        gelu.  The tensor-core and the streaming products apply it in their epilogues."""
+        gelu.  The tensor-core and the streaming products apply it in their epilogues.  `limit` = L: the clamped gate
+        instead, a = g' sigmoid(1.702 g') (u' + 1) with g' = min(g, L), u' = clamp(u, -L, L), applied to the plain
+        product's rows by a kernel of its own."""
         a = torch.empty((x.shape[0], F), dtype=x.dtype, device=x.device)
+        if limit is not None:
+            gu = self.linear(x, w_gate_up)
+            kernels.swiglu(a, gu, act=kernels.ACT_CLAMPED_SWISH, limit=limit)
+            return a
         flag = 2 if gelu else True
         kind = self._product_kernel(x, w_gate_up)
         # From 9 rows on the tcgen05 few-rows kernel leads (measured on B200 at 16 rows, us, streaming /
@@ -292,7 +298,7 @@ class Runtime:
     TCGEN05_ATTENTION_MIN_LEN_BATCH = 256    # ... unless there are many of them:
     TCGEN05_ATTENTION_MIN_TOKENS = 2048      # this many rows in the step
 
-    def attention_prefill(self, ctx, q, k, v, gate, batch, QH, KVH, HD, window, scale, sink=None):
+    def attention_prefill(self, ctx, q, k, v, gate, batch, QH, KVH, HD, window, scale, sink=None, softcap=0.0):
         """Attention of a prompt step over the step's own keys and values.  bfloat16 with head size
         64 or 128 and long sequences: the tcgen05 kernel (measured on B200, 32 heads of 64, tcgen05 against
         mma.sync: 18 / 25 us at 768 tokens, 22 / 35 at 1,024, 40 / 96 at 2,048, 664 against 264 TFLOP/s at
@@ -310,10 +316,10 @@ class Runtime:
         if (bf16 and aligned and HD in (64, 128) and long_enough
                 and ctx.stride(0) % 8 == 0 and ctx.data_ptr() % 16 == 0):
             kernels.attn_prefill_tc(ctx, q, k, v, gate, batch.seq_start, batch.B, batch.max_len, QH, KVH, HD, window,
-                                    scale, err=self.error_flag, sink=sink)
+                                    scale, err=self.error_flag, sink=sink, softcap=softcap)
             return
         fn = kernels.attn_prefill_mma if (bf16 and aligned and HD % 16 == 0 and HD <= 128) else kernels.attn_prefill_simt
-        fn(ctx, q, k, v, gate, batch.seq_start, batch.B, batch.max_len, QH, KVH, HD, window, scale, sink=sink)
+        fn(ctx, q, k, v, gate, batch.seq_start, batch.B, batch.max_len, QH, KVH, HD, window, scale, sink=sink, softcap=softcap)
 
     # Measured on B200, 32 heads of 64 over 8 kv heads, mma.sync against tcgen05:
     # 128 rows on 512 held tokens 20.9 / 17.0 us, on 256 held 13.4 / 13.3; 64 rows on 256 held 12.1 / 13.2; 16 rows x 8
@@ -322,7 +328,7 @@ class Runtime:
     TCGEN05_APPEND_MIN_ROWS = 8
     TCGEN05_APPEND_MIN_SPAN = 512
 
-    def attention_append(self, ctx, q, k, v, gate, batch, state, QH, KVH, HD, window, scale, sink=None):
+    def attention_append(self, ctx, q, k, v, gate, batch, state, QH, KVH, HD, window, scale, sink=None, softcap=0.0):
         """Attention of a step whose sequences already hold tokens: keys and values below each
         sequence's first position of the step come from the paged cache, the rest from the step's own
         rows (written to the cache by the caller afterwards).  The choice of kernel follows
@@ -337,8 +343,8 @@ class Runtime:
                 and batch.max_len >= self.TCGEN05_APPEND_MIN_ROWS and ctx.stride(0) % 8 == 0 and ctx.data_ptr() % 16 == 0):
             kernels.attn_append_tc(ctx, q, k, v, gate, batch.seq_start, batch.seq_pos0, batch.seq_slot, state.pool,
                                    state.pages, state.ptab, state.ring, batch.B, batch.max_len, QH, KVH, HD, window,
-                                   scale, err=self.error_flag, sink=sink)
+                                   scale, err=self.error_flag, sink=sink, softcap=softcap)
             return
         kernels.attn_append(ctx, q, k, v, gate, batch.seq_start, batch.seq_pos0, batch.seq_slot, state.pool,
                             state.pages, state.ptab, state.ring, batch.B, batch.max_len, QH, KVH, HD, window, scale,
-                            tensor_cores=self.tensor_core_prompts, sink=sink)
+                            tensor_cores=self.tensor_core_prompts, sink=sink, softcap=softcap)

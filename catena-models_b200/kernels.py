@@ -26,7 +26,7 @@ _SIGNATURES = {
     "cm_add_norm": [_i, _vp, _vp, _vp, _vp, _i, _ll, _vp, _vp, _vp, _i, _i, _f, _f, _vp],
     "cm_gemm_tc_few_rows_parts": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp],
     "cm_gemm_skinny_parts": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _ll, _i, _vp],
-    "cm_swiglu": [_i, _vp, _vp, _i, _i, _i, _vp],
+    "cm_swiglu": [_i, _vp, _vp, _i, _i, _i, _f, _vp],
     "cm_gather_rows": [_i, _vp, _vp, _vp, _i, _i, _vp],
     "cm_gemm_simt": [_i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
     "cm_gemm_skinny": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp],
@@ -34,19 +34,19 @@ _SIGNATURES = {
     "cm_gemm_tc_few_rows": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _vp],
     "cm_qk_prepare": [_i, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i,
                       _i, _f, _i, _f, _i, _vp],
-    "cm_attn_prefill_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
-    "cm_attn_prefill_mma": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
-    "cm_attn_prefill_tc": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _ll, _i, _i, _i, _i, _f, _vp, _vp, _vp],
+    "cm_attn_prefill_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _vp],
+    "cm_attn_prefill_mma": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _vp],
+    "cm_attn_prefill_tc": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _ll, _i, _i, _i, _i, _f, _f, _vp, _vp, _vp],
     "cm_attn_decode": [_i, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _i,
-                       _i, _f, _vp, _vp, _vp, _vp],
+                       _i, _f, _f, _vp, _vp, _vp, _vp],
     "cm_gemm_skinny_shortconv": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _vp],
     "cm_shortconv": [_i, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "cm_attn_append_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i,
-                            _i, _i, _i, _f, _vp, _vp],
+                            _i, _i, _i, _f, _f, _vp, _vp],
     "cm_attn_append_mma": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _i,
-                           _i, _i, _f, _vp, _vp],
+                           _i, _i, _f, _f, _vp, _vp],
     "cm_attn_append_tc": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _ll, _i,
-                          _i, _i, _i, _f, _vp, _vp, _vp],
+                          _i, _i, _i, _f, _f, _vp, _vp, _vp],
     "cm_gemm_tc_parts": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _i, _vp, _vp],
     "cm_kv_store": [_i, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _vp],
     "cm_sample": [_vp, _vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp],
@@ -68,7 +68,7 @@ _SIGNATURES = {
     "cm_decay_from_logits": [_vp, _vp, _vp, _ll, _i, _i, _f, _vp],
     "cm_matrix_scan": [_i, _i, _vp, _i, _vp],
     "cm_lightning_chunked": [_i, _vp, _i, _i, _vp, _vp],
-    "cm_moe_route": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _f, _f, _vp],
+    "cm_moe_route": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _f, _f, _i, _vp],
     "cm_moe_identity": [_i, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
     "cm_latent_prepare": [_i, _vp, _vp],
     "cm_latent_query_turn": [_i, _vp, _vp],
@@ -78,7 +78,7 @@ _SIGNATURES = {
     "cm_head_linear": [_i, _vp, _vp, _vp, _ll, _i, _i, _i, _ll, _ll, _i, _i, _i, _i, _vp],
     "cm_moe_gather": [_i, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
     "cm_gemm_tc_grouped": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _i, _vp, _vp],
-    "cm_moe_grouped": [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "cm_moe_grouped": [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
 }
 
 
@@ -409,10 +409,20 @@ def scale_softcap(logits, scale=1.0, cap=0.0):
     _check(lib().cm_scale_softcap(_ptr(logits), logits.numel(), scale, cap, _stream()), "scale_softcap")
 
 
-def swiglu(out, gate_up, gelu=False):
-    """out = act(gate) * up for the packed rows [gate | up]; act: silu, or the tanh form of gelu."""
+ACT_SILU, ACT_GELU_TANH, ACT_CLAMPED_SWISH = 0, 1, 2       # csrc/common.cuh: gated_act
+ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "clamped_swish": ACT_CLAMPED_SWISH}
+
+
+def swiglu(out, gate_up, gelu=False, act=None, limit=0.0):
+    """out = act(gate, up) for the packed contiguous rows [gate | up].  act: ACT_SILU silu(g) u (the default), ACT_GELU_TANH
+    (or `gelu`) the tanh form of gelu on g, times u; ACT_CLAMPED_SWISH: with g' = min(g, limit) and u' = clamp(u, -limit,
+    limit), g' sigmoid(1.702 g') (u' + 1)."""
     rows, F = out.shape
-    _check(lib().cm_swiglu(dtype_code(out.dtype), _ptr(out), _ptr(gate_up), rows, F, int(gelu), _stream()), "swiglu")
+    act = (ACT_GELU_TANH if gelu else ACT_SILU) if act is None else int(act)
+    if not gate_up.is_contiguous() or gate_up.shape != (rows, 2 * F) or not out.is_contiguous():
+        raise KernelError("swiglu: contiguous rows [gate | up]")
+    _check(lib().cm_swiglu(dtype_code(out.dtype), _ptr(out), _ptr(gate_up), rows, F, act, float(limit), _stream()), "swiglu",
+           cost=lambda: (f"{rows}x{F}", _nbytes(out, gate_up), 8 * rows * F))
 
 
 def gather_rows(out, x, rows):
@@ -566,31 +576,32 @@ def qk_prepare(qkv, wq, wk, rate, tok_pos, tok_seq, seq_slot, seq_end, pool, pag
                          T * HD * qkv.element_size() * (2 * QH + (2 * KVH if pool is None else 4 * KVH)), 0))
 
 
-def attn_prefill_simt(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale, sink=None):
+def attn_prefill_simt(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale, sink=None, softcap=0.0):
     """q, k, v, gate are column views of one packed row-major buffer (same row stride).  `sink` (all
     attention kernels): float32 [QH], a learned logit per query head that joins the softmax's denominator
-    and nothing else (it has no key and no value), or None."""
+    and nothing else (it has no key and no value), or None.  `softcap` (all attention kernels) = c > 0: every
+    score is bounded before the mask and the softmax, s <- c * tanh(s / c) with s = (q . k) * scale."""
     if not (q.stride(0) == k.stride(0) == v.stride(0)):
         raise KernelError("attn_prefill: q, k and v must share a row stride")
     _check(lib().cm_attn_prefill_simt(dtype_code(q.dtype), _ptr(ctx), ctx.stride(0), _ptr(q), _ptr(k), _ptr(v),
                                       q.stride(0), _ptr(gate), 0 if gate is None else gate.stride(0),
-                                      _ptr(seq_start), B, max_len, QH, KVH, HD, window, scale, _ptr(sink), _stream()),
+                                      _ptr(seq_start), B, max_len, QH, KVH, HD, window, scale, softcap, _ptr(sink), _stream()),
            "attn_prefill_simt",
            cost=lambda: (f"{B} sequences up to {max_len}, {QH}/{KVH} heads of {HD}, window {window}", 0, 0))
 
 
-def attn_prefill_mma(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale, sink=None):
+def attn_prefill_mma(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale, sink=None, softcap=0.0):
     """The same on the tensor cores: bfloat16, head sizes that are multiples of 16 up to 128."""
     if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.dtype != torch.bfloat16:
         raise KernelError("attn_prefill_mma: bfloat16 q, k and v that share a row stride")
     _check(lib().cm_attn_prefill_mma(_ptr(ctx), ctx.stride(0), _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gate),
                                      0 if gate is None else gate.stride(0), _ptr(seq_start), B, max_len, QH, KVH,
-                                     HD, window, scale, _ptr(sink), _stream()), "attn_prefill_mma",
+                                     HD, window, scale, softcap, _ptr(sink), _stream()), "attn_prefill_mma",
            cost=lambda: (f"{B} sequences up to {max_len}, {QH}/{KVH} heads of {HD}, window {window}", 0, 0))
 
 
 def attn_append(ctx, q, k, v, gate, seq_start, seq_pos0, seq_slot, pool, pages, ptab, ring, B, max_len, QH, KVH, HD,
-                window, scale, tensor_cores=True, sink=None):
+                window, scale, tensor_cores=True, sink=None, softcap=0.0):
     """Attention of a step whose sequences may stand at seq_pos0[b] > 0: keys and values below that
     position come from the paged cache `pool`, the rest from the step's own rows (q, k, v as for the
     prefill kernels), which the caller writes to the cache afterwards (`kv_store`).  bfloat16 with a
@@ -601,7 +612,7 @@ def attn_append(ctx, q, k, v, gate, seq_start, seq_pos0, seq_slot, pool, pages, 
            and (q.data_ptr() | k.data_ptr() | v.data_ptr() | pool.data_ptr()) % 16 == 0)
     common = (_ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gate), 0 if gate is None else gate.stride(0), _ptr(seq_start),
               _ptr(seq_pos0), _ptr(seq_slot), _ptr(pool), pages, _ptr(ptab), ptab.stride(0), ring, B, max_len, QH, KVH,
-              HD, window, scale, _ptr(sink), _stream())
+              HD, window, scale, softcap, _ptr(sink), _stream())
     if mma:
         _check(lib().cm_attn_append_mma(_ptr(ctx), ctx.stride(0), *common), "attn_append_mma")
     else:
@@ -609,7 +620,7 @@ def attn_append(ctx, q, k, v, gate, seq_start, seq_pos0, seq_slot, pool, pages, 
 
 
 def attn_append_tc(ctx, q, k, v, gate, seq_start, seq_pos0, seq_slot, pool, pages, ptab, ring, B, max_len, QH, KVH, HD,
-                   window, scale, err=None, sink=None):
+                   window, scale, err=None, sink=None, softcap=0.0):
     """`attn_append` on the tcgen05 tensor cores: bfloat16, head size 64 or 128, the cache read page by
     page with TMA.  err: device int32 that a block raises if a bounded pipeline wait runs out."""
     if (not (q.stride(0) == k.stride(0) == v.stride(0)) or q.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16
@@ -620,7 +631,7 @@ def attn_append_tc(ctx, q, k, v, gate, seq_start, seq_pos0, seq_slot, pool, page
     _check(lib().cm_attn_append_tc(_ptr(ctx), ctx.stride(0), _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gate),
                                    0 if gate is None else gate.stride(0), _ptr(seq_start), _ptr(seq_pos0),
                                    _ptr(seq_slot), _ptr(pool), pages, _ptr(ptab), ptab.stride(0), ring, B, max_len,
-                                   q.shape[0], QH, KVH, HD, window, scale, _ptr(sink), _ptr(err), _stream()), "attn_append_tc",
+                                   q.shape[0], QH, KVH, HD, window, scale, softcap, _ptr(sink), _ptr(err), _stream()), "attn_append_tc",
            cost=lambda: (f"{B} sequences of up to {max_len} rows, {QH}/{KVH} heads of {HD}, window {window}", 0, 0))
 
 
@@ -633,7 +644,7 @@ def kv_store(kv, tok_pos, tok_seq, seq_slot, seq_end, pool, pages, ptab, ring, K
            "kv_store")
 
 
-def attn_prefill_tc(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale, err=None, sink=None):
+def attn_prefill_tc(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale, err=None, sink=None, softcap=0.0):
     """The same on the tcgen05 tensor cores (TMA-fed, scores and outputs in tensor memory): bfloat16,
     head size 64 or 128.  q, k and v are column blocks of one row-major buffer.  err: device int32
     that a block raises if one of its bounded pipeline waits runs out."""
@@ -641,7 +652,7 @@ def attn_prefill_tc(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, wind
         raise KernelError("attn_prefill_tc: bfloat16 q, k and v that share rows and a row stride")
     _check(lib().cm_attn_prefill_tc(_ptr(ctx), ctx.stride(0), _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gate),
                                     0 if gate is None else gate.stride(0), _ptr(seq_start), B, max_len, q.shape[0],
-                                    QH, KVH, HD, window, scale, _ptr(sink), _ptr(err), _stream()), "attn_prefill_tc",
+                                    QH, KVH, HD, window, scale, softcap, _ptr(sink), _ptr(err), _stream()), "attn_prefill_tc",
            cost=lambda: (f"{B} sequences up to {max_len}, {QH}/{KVH} heads of {HD}, window {window}", 0, 0))
 
 
@@ -665,11 +676,11 @@ def attn_decode_scratch(B, QH, HD, n_chunks, device):
 
 
 def attn_decode(ctx, q, gate, seq_pos, seq_slot, pool, pages, ptab, ring, window, QH, KVH, HD, n_chunks,
-                scale, part_o, part_ml, sink=None):
+                scale, part_o, part_ml, sink=None, softcap=0.0):
     B = q.shape[0]
     _check(lib().cm_attn_decode(dtype_code(q.dtype), _ptr(ctx), ctx.stride(0), _ptr(q), q.stride(0), _ptr(gate),
                                 0 if gate is None else gate.stride(0), _ptr(seq_pos), _ptr(seq_slot), _ptr(pool),
-                                pages, _ptr(ptab), ptab.stride(0), ring, window, B, QH, KVH, HD, n_chunks, scale,
+                                pages, _ptr(ptab), ptab.stride(0), ring, window, B, QH, KVH, HD, n_chunks, scale, softcap,
                                 _ptr(part_o), _ptr(part_ml), _ptr(sink), _stream()), "attn_decode", 2,
            cost=lambda: (f"{B} sequences, {QH}/{KVH} heads of {HD}, window {window}, {n_chunks} chunks", 0, 0))
 
@@ -964,16 +975,21 @@ class _TapRotArgs(ctypes.Structure):
                 ("q_out", _vp), ("ldq", _ll), ("pool", _vp), ("pages", _ll), ("ptab", _vp), ("ptab_stride", _ll),
                 ("rate", _vp), ("mag", _f), ("tok_seq", _vp), ("tok_pos", _vp), ("seq_start", _vp), ("seq_pos0", _vp),
                 ("seq_slot", _vp)] + [(n, _i) for n in ("T", "B", "QC", "KC", "VC", "K", "sub", "rot", "G", "KW", "DV", "HDC",
-                                                        "one_token_each")]
+                                                        "one_token_each", "interleaved", "value_from_key", "ring",
+                                                        "no_store", "rows_out")]
 
 
-def tap_rotate_store(proj, bias, taps, state, q_out, batch, q_channels, sub, rate, mag, kv=None, one_token_each=False):
+def tap_rotate_store(proj, bias, taps, state, q_out, batch, q_channels, sub, rate, mag, kv=None, one_token_each=False,
+                     interleaved=False, value_from_key=False, ring=0, store=True, rows_out=False):
     """Short causal taps over the leading channels of the projected rows `proj` (q, then k and v when this layer
     has them), the partial rotation of q and k, and the cache write.  bias float32 [C] or None; taps float32
     [C, K]; state float32 [slots, >= K C] (a ring of the last K projected rows of every sequence, moved on by
     this call); q_out [T, q_channels] receives the queries.  `sub`: channels of one rotated vector; rate float32
     [rot / 2] or None; mag: the factor on sine and cosine.  kv = (pool, pages, ptab, G, key row width, value row
-    width): this layer's pages [2, pages, G, PAGE_TOKENS, HDC]; keys and values follow q in `proj`."""
+    width): this layer's pages [2, pages, G, PAGE_TOKENS, HDC]; keys and values follow q in `proj`.
+    `interleaved`: the rotation pairs channel 2i with 2i + 1.  `value_from_key`: there are no value channels (value
+    row width 0 in `kv`); a position's value is its key before the rotation.  `ring`: the pages are a ring of that many
+    entries.  `store` False leaves the cache alone.  `rows_out`: q_out rows are [q | turned k | v]."""
     T = proj.shape[0]
     C, K = taps.shape
     G = KW = DV = HDC = 0
@@ -984,15 +1000,20 @@ def tap_rotate_store(proj, bias, taps, state, q_out, batch, q_channels, sub, rat
         HDC = pool.shape[-1]
     if C != q_channels + G * (KW + DV) or proj.shape[1] < C or proj.stride(1) != 1 or q_out.dtype != proj.dtype:
         raise KernelError("tap_rotate_store: the projected rows do not hold the channels that the taps name")
-    if not (taps.is_contiguous() and taps.dtype == state.dtype == torch.float32 and state.stride(-1) == 1):
+    if not (taps.is_contiguous() and taps.dtype == torch.float32) or (K > 1 and state is None):
+        raise KernelError("tap_rotate_store: float32 taps, and a state for more than one tap")
+    if state is not None and (state.dtype != torch.float32 or state.stride(-1) != 1):
         raise KernelError("tap_rotate_store: float32 taps and state")
+    if q_out.shape[1] < (C + (G * KW if value_from_key else 0) if rows_out else q_channels):
+        raise KernelError("tap_rotate_store: the output rows are too short")
     a = _TapRotArgs(proj=_ptr(proj), ldp=proj.stride(0), bias=_ptr(bias), taps=_ptr(taps), state=_ptr(state),
-                    state_stride=state.stride(0), q_out=_ptr(q_out), ldq=q_out.stride(0), pool=_ptr(pool), pages=pages,
+                    state_stride=0 if state is None else state.stride(0), q_out=_ptr(q_out), ldq=q_out.stride(0), pool=_ptr(pool), pages=pages,
                     ptab=_ptr(ptab), ptab_stride=0 if ptab is None else ptab.stride(0), rate=_ptr(rate), mag=mag,
                     tok_seq=_ptr(batch.tok_seq), tok_pos=_ptr(batch.tok_pos), seq_start=_ptr(batch.seq_start),
                     seq_pos0=_ptr(batch.seq_pos0), seq_slot=_ptr(batch.seq_slot), T=T, B=batch.B, QC=q_channels,
                     KC=G * KW, VC=G * DV, K=K, sub=sub, rot=0 if rate is None else 2 * rate.numel(), G=G, KW=KW, DV=DV,
-                    HDC=HDC, one_token_each=int(one_token_each))
+                    HDC=HDC, one_token_each=int(one_token_each), interleaved=int(interleaved),
+                    value_from_key=int(value_from_key), ring=int(ring), no_store=int(not store), rows_out=int(rows_out))
     _check(lib().cm_tap_rotate_store(dtype_code(proj.dtype), ctypes.byref(a), _stream()), "tap_rotate_store",
            1 if one_token_each or K < 2 else 2,
            cost=lambda: (f"{T}x{C}, {K} taps", 2 * T * C * proj.element_size(), 2 * K * T * C))
@@ -1082,7 +1103,7 @@ class _LatentArgs(ctypes.Structure):
                 ("eps", _f), ("scale", _f), ("rows", _ll), ("tok_pos", _vp), ("tok_seq", _vp), ("seq_start", _vp),
                 ("seq_pos0", _vp), ("seq_end", _vp), ("seq_slot", _vp), ("pool", _vp), ("ptab", _vp), ("ptab_stride", _ll),
                 ("B", _i), ("max_len", _i), ("splits", _i), ("chunk", _i), ("parts", _vp), ("ckv", _vp), ("kvu", _vp),
-                ("ld_kvu", _ll), ("qkv", _vp), ("ld_qkv", _ll), ("HD", _i), ("DV", _i)]
+                ("ld_kvu", _ll), ("qkv", _vp), ("ld_qkv", _ll), ("HD", _i), ("DV", _i), ("mag", _f), ("no_entry", _i)]
 
 
 latent_decode_tensor_cores = True   # off: single-token steps of the latent attention stay on the CUDA cores (tests compare)
@@ -1101,21 +1122,24 @@ def latent_entry_size(kv_rank, rot_dim):
     return -(-(kv_rank + rot_dim) // 8) * 8
 
 
-def _latent_args(batch, pool, ptab, H, D, R, KR, QR, eps=0.0, scale=1.0, **fields):
-    return _LatentArgs(H=H, D=D, R=R, KR=KR, QR=QR, E=KR + R, EC=pool.shape[-1], eps=eps, scale=scale, rows=batch.T,
+def _latent_args(batch, pool, ptab, H, D, R, KR, QR, eps=0.0, scale=1.0, mag=1.0, **fields):
+    return _LatentArgs(mag=mag, H=H, D=D, R=R, KR=KR, QR=QR, E=KR + R, EC=pool.shape[-1], eps=eps, scale=scale, rows=batch.T,
                        tok_pos=_ptr(batch.tok_pos), tok_seq=_ptr(batch.tok_seq), seq_start=_ptr(batch.seq_start),
                        seq_pos0=_ptr(batch.seq_pos0), seq_end=_ptr(batch.seq_end), seq_slot=_ptr(batch.seq_slot),
                        pool=_ptr(pool), ptab=_ptr(ptab), ptab_stride=ptab.stride(0), B=batch.B, max_len=batch.max_len,
                        splits=1, chunk=0, **fields)
 
 
-def latent_prepare(cq, proj, q_off, kv_off, wq_norm, wkv_norm, rate, pool, ptab, batch, H, D, R, KR, QR, eps, entries=None):
+def latent_prepare(cq, proj, q_off, kv_off, wq_norm, wkv_norm, rate, pool, ptab, batch, H, D, R, KR, QR, eps, entries=None,
+                   mag=1.0, make_entry=True):
     """Per row of the step: cq = norm(proj[q_off : q_off + QR]) * wq_norm (activation dtype, for the product that
     makes the heads' queries), and the row's cache entry [norm(proj[kv_off : kv_off + KR]) * wkv_norm | the next R
     channels turned by the position (pairs 2i, 2i + 1 by position * rate[i]) | zeros] into pool [pages, PAGE_TOKENS, EC]
     through the page table.  Norms and angles are float32.  `entries` [rows, EC] (contiguous): the same entries once
-    more in the order of the step's rows (zeros for rows of padding), for a product over them."""
-    a = _latent_args(batch, pool, ptab, H, D, R, KR, QR, eps=eps, proj=_ptr(proj), ld_proj=proj.stride(0), q_off=q_off,
+    more in the order of the step's rows (zeros for rows of padding), for a product over them.  `mag`: the factor on
+    sine and cosine (all rotations of the latent attention take it).  `make_entry` False: only cq is made (a layer that
+    reads another layer's entries; kv_off and wkv_norm are then not used)."""
+    a = _latent_args(batch, pool, ptab, H, D, R, KR, QR, eps=eps, mag=mag, no_entry=int(not make_entry), proj=_ptr(proj), ld_proj=proj.stride(0), q_off=q_off,
                      kv_off=kv_off, cq=_ptr(cq), wq_norm=_ptr(wq_norm), wkv_norm=_ptr(wkv_norm), rate=_ptr(rate),
                      ckv=_ptr(entries))
     if proj.stride(1) != 1 or not cq.is_contiguous() or cq.dtype != proj.dtype or pool.dtype != proj.dtype:
@@ -1126,22 +1150,23 @@ def latent_prepare(cq, proj, q_off, kv_off, wq_norm, wkv_norm, rate, pool, ptab,
            cost=lambda: (f"{batch.T} rows, {QR} + {KR} + {R}", batch.T * (2 * QR + 2 * (KR + R)) * proj.element_size(), 6 * batch.T * (QR + KR)))
 
 
-def latent_query_turn(qa, q, rate, pool, ptab, batch, H, D, R, KR):
+def latent_query_turn(qa, q, rate, pool, ptab, batch, H, D, R, KR, mag=1.0):
     """qa[t, h, KR:KR + R] (float32) = the last R channels of head h's query q[t, h, :D + R], turned by the position."""
-    a = _latent_args(batch, pool, ptab, H, D, R, KR, 0, q=_ptr(q), ldq=q.stride(0), qa=_ptr(qa), ldqa=qa.stride(0), rate=_ptr(rate))
+    a = _latent_args(batch, pool, ptab, H, D, R, KR, 0, mag=mag, q=_ptr(q), ldq=q.stride(0), qa=_ptr(qa), ldqa=qa.stride(0),
+                     rate=_ptr(rate))
     if qa.dtype != torch.float32 or qa.stride(1) != 1 or q.stride(1) != 1:
         raise KernelError("latent_query_turn: float32 rows for the turned queries")
     _check(lib().cm_latent_query_turn(dtype_code(q.dtype), ctypes.byref(a), _stream()), "latent_query_turn",
            cost=lambda: (f"{batch.T} rows, {H} heads of {R}", batch.T * H * R * (4 + q.element_size()), 6 * batch.T * H * R))
 
 
-def latent_expand(qkv, q, kvu, entries, rate, pool, ptab, batch, H, D, R, DV, KR, HD):
+def latent_expand(qkv, q, kvu, entries, rate, pool, ptab, batch, H, D, R, DV, KR, HD, mag=1.0):
     """The operands of an attention over keys and values per head, for a prompt step: qkv [rows, 3 * H * HD] =
     per head [q_plain | q_turn turned by the position | 0], then per head [kvu's unturned key | the row's turned key
     part from `entries` | 0], then per head [kvu's value | 0].  q [rows, H * (D + R)] as the product left it; kvu
     [rows, H * D + H * DV] = [W_uk; W_uv] times the row's latent; entries [rows, EC] from `latent_prepare`.  Rows of
     padding become zeros."""
-    a = _latent_args(batch, pool, ptab, H, D, R, KR, 0, q=_ptr(q), ldq=q.stride(0), rate=_ptr(rate), ckv=_ptr(entries),
+    a = _latent_args(batch, pool, ptab, H, D, R, KR, 0, mag=mag, q=_ptr(q), ldq=q.stride(0), rate=_ptr(rate), ckv=_ptr(entries),
                      kvu=_ptr(kvu), ld_kvu=kvu.stride(0), qkv=_ptr(qkv), ld_qkv=qkv.stride(0), HD=HD, DV=DV)
     if (qkv.shape[1] != 3 * H * HD or kvu.shape[1] != H * (D + DV) or q.shape[1] != H * (D + R) or not entries.is_contiguous()
             or any(t.stride(1) != 1 or t.dtype != qkv.dtype for t in (qkv, q, kvu, entries))):
@@ -1233,7 +1258,7 @@ def moe_tile_group(work, pairs, experts, tile_rows):
 
 def moe_route(ids, wts, perm, dest, work, h, w_router, tok_seq, top, softmax_gate=False, renormalize=False,
               tile_rows=MOE_TILE_SIMT, xs=None, apply_weight=False, correction=None, groups=0, keep=0, identity=0, scale=1.0,
-              renorm_eps=0.0):
+              renorm_eps=0.0, group_best=1):
     """Scores of every token's experts in float32 (sigmoid, or softmax over the experts), the `top` best
     (ids, wts: [rows * top]; -1 for rows of padding), and the pairs in the order of their experts, every expert's
     rows beginning a row tile of `tile_rows` rows: perm[sorted row] = pair (moe_max_tiles * tile_rows entries),
@@ -1241,7 +1266,8 @@ def moe_route(ids, wts, perm, dest, work, h, w_router, tok_seq, top, softmax_gat
     ([moe_max_tiles * tile_rows, W]) the experts' inputs are gathered into it in the same call (`moe_gather`).  A step of
     up to 64 rows runs all of this in one launch of one block.
     `correction` (float32 [E]): added to the scores for the choice only.  `groups`, `keep`: the experts form `groups` equal
-    groups of neighbours, and only experts of the `keep` groups with the largest best choice score can be chosen.
+    groups of neighbours, and only experts of the `keep` groups with the largest score can be chosen; a group's score is
+    the sum of its `group_best` largest choice scores (1: its largest).
     `identity`: the last `identity` router outputs are experts without matrices whose output is their input: their pairs get
     a weight and dest -1 (`moe_identity` adds them).  `scale`: a factor on the weights; `renorm_eps`: added to the sum that
     `renormalize` divides by."""
@@ -1254,7 +1280,7 @@ def moe_route(ids, wts, perm, dest, work, h, w_router, tok_seq, top, softmax_gat
     _check(lib().cm_moe_route(dtype_code(h.dtype), _ptr(ids), _ptr(wts), _ptr(perm), _ptr(dest), _ptr(work), _ptr(h),
                               _ptr(w_router), _ptr(tok_seq), rows, W, E, top, int(softmax_gate), int(renormalize), tile_rows,
                               _ptr(xs), int(apply_weight), _ptr(correction), int(groups), int(keep), int(identity), float(scale),
-                              float(renorm_eps), _stream()), "moe_route",
+                              float(renorm_eps), int(group_best), _stream()), "moe_route",
            1 if rows <= 64 and rows * E * (2 if correction is not None or groups else 1) <= 8192 else (4 if xs is not None else 3),
            cost=lambda: (f"{rows}x{W} over {E}, top {top}", _nbytes(h, w_router), 2 * rows * E * W))
 
@@ -1274,17 +1300,18 @@ def moe_gather(xs, h, dest, wts, top, apply_weight):
                                _stream()), "moe_gather", cost=lambda: (f"{pairs}x{K}", 2 * pairs * K * h.element_size(), pairs * K))
 
 
-def moe_grouped(out, x, w, work, perm, wts, top, max_tiles, up, apply_weight, gelu=False):
+def moe_grouped(out, x, w, work, perm, wts, top, max_tiles, up, apply_weight, gelu=False, act=None, limit=0.0):
     """The experts' products over the rows that `moe_route` gave them (row tiles of 32), on the CUDA cores.
     up: out[sorted row] = act(Wg x) * (Wu x) with x = h[token] (times the pair's weight if apply_weight), w [E, 2 F, K];
-    else out[sorted row] (float32) = Wd a (times the weight if apply_weight), w [E, N, K]."""
+    else out[sorted row] (float32) = Wd a (times the weight if apply_weight), w [E, N, K].  `act`, `limit`: as `swiglu`."""
+    act = (ACT_GELU_TANH if gelu else ACT_SILU) if act is None else int(act)
     E = w.shape[0]
     N = w.shape[1] // 2 if up else w.shape[1]
     K = w.shape[2]
     if w.dtype != x.dtype or not (x.is_contiguous() and w.is_contiguous() and out.is_contiguous()) or x.shape[1] != K:
         raise KernelError("moe_grouped: contiguous operands of one dtype")
     _check(lib().cm_moe_grouped(dtype_code(x.dtype), int(up), _ptr(out), _ptr(x), _ptr(w), _ptr(work), _ptr(perm), _ptr(wts),
-                                E, top, max_tiles, N, K, int(apply_weight), int(gelu), _stream()),
+                                E, top, max_tiles, N, K, int(apply_weight), act, float(limit), _stream()),
            "moe_grouped_" + ("up" if up else "down"),
            cost=lambda: (f"{out.shape[0]} rows, {w.shape[1]}x{K} per expert", _nbytes(x, out) + min(E, out.shape[0]) * w[0].numel() * w.element_size(),
                          2 * out.shape[0] * w.shape[1] * K))

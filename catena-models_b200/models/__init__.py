@@ -1,2 +1,2 @@
 """Architectures.  Importing this package registers them by name."""
-from . import fozedra, lfm3, maferax, narasun  # noqa: F401
+from . import fozedra, lfm3, maferax, narasun, relilix  # noqa: F401

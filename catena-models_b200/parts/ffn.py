@@ -14,15 +14,19 @@ class SwiGLU(FeedForward):
     fused_decode_ok = True
     supports_append = True
 
-    def __init__(self, prefix, hidden, intermediate, names=None, out_dtype=None, activation="silu"):
+    def __init__(self, prefix, hidden, intermediate, names=None, out_dtype=None, activation="silu", limit=0.0):
         """out_dtype "float32": the down projection's result stays in float (for a float residual stream).
-        activation: what the gate passes through, "silu" or "gelu_tanh" (the tanh form of gelu)."""
+        activation: what the gate passes through, "silu" or "gelu_tanh" (the tanh form of gelu), or "clamped_swish" with
+        `limit` L: a = g' sigmoid(1.702 g') (u' + 1) with g' = min(g, L), u' = clamp(u, -L, L)."""
         import torch
 
-        if activation not in ("silu", "gelu_tanh"):
-            raise ValueError("SwiGLU: activation silu|gelu_tanh")
+        if activation not in ("silu", "gelu_tanh", "clamped_swish"):
+            raise ValueError("SwiGLU: activation silu|gelu_tanh|clamped_swish")
+        if activation == "clamped_swish" and not limit > 0.0:
+            raise ValueError("SwiGLU: the clamped gate needs its limit")
         self.gelu = activation == "gelu_tanh"
-        if self.gelu:
+        self.clamped, self.limit = activation == "clamped_swish", float(limit)
+        if self.gelu or self.clamped:
             self.fused_decode_ok = False         # the persistent decode kernel's gated product has silu only
         self.out_dtype = {None: None, "float32": torch.float32}[out_dtype]
         names = names or {}
@@ -36,7 +40,8 @@ class SwiGLU(FeedForward):
         return [self.gate_up, self.down]
 
     def forward(self, rt, batch, x):
-        a = rt.gate_up_swiglu(x, self.gate_up.weight, self.intermediate, gelu=self.gelu)
+        a = rt.gate_up_swiglu(x, self.gate_up.weight, self.intermediate, gelu=self.gelu,
+                              limit=self.limit if self.clamped else None)
         return self.down.apply(rt, a, out_dtype=self.out_dtype, partial_ok=batch.partial_sums_ok and self.out_dtype is None)
 
 
@@ -65,5 +70,31 @@ class ReluSquared(FeedForward):
         return self.down.apply(rt, a, out_dtype=self.out_dtype, partial_ok=batch.partial_sums_ok and self.out_dtype is None)
 
 
+class SumOfFeedForwards(FeedForward):
+    """Several feed-forwards that read the same input; the result is the sum of theirs (a routed feed-forward and an
+    expert that every token runs, say).  Each member hands over a tensor or `kernels.Terms`; the block's residual sum
+    adds all pieces in the members' order."""
+    prompt_capturable = True
+    supports_append = True
+
+    def __init__(self, members):
+        self.members = list(members)
+        if not self.members:
+            raise ValueError("SumOfFeedForwards: no members")
+
+    def children(self):
+        return self.members
+
+    def forward(self, rt, batch, x):
+        from .. import kernels
+
+        out = kernels.Terms()
+        for member in self.members:
+            y = member.forward(rt, batch, x)
+            out += y if isinstance(y, kernels.Terms) else [(y, 1.0, 1)]
+        return out
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "sum", SumOfFeedForwards)
 register_part("feed_forward", "relu_squared", ReluSquared)

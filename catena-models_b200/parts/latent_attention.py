@@ -19,7 +19,13 @@ W_uv behind the weighted sum over the latents, each a product with one matrix pe
 Norms, angles, scores, softmax and the sums over the latents are float32.
 
 The position encoding turns the leading `position.dims` channels of the rot_dim part in interleaved pairs; further
-channels of that part pass unchanged.
+channels of that part pass unchanged.  A position encoding with a `magnitude` has it on every sine and cosine, of the
+queries' turned part and of the cached key part alike.
+
+`shares_latents`: the layer has no W_dkv.  It reads the entries [c | r] that another layer of the same latent size and
+rotation wrote (the plan hands it that layer's state unit, `owns_state=False`), with its own W_uk, W_uv, queries and
+gate; in a whole-prompt step of the expanded form it takes the owner's side-by-side copy of the step's entries from
+`StepBatch.shared`.
 
 Every kind of step writes its entries to the cache first.  Portions, single tokens and mixed lengths then read all
 keys from there (`kernels.latent_attn`, CUDA cores, float32 sums).  A bfloat16 step of whole prompts has a second form:
@@ -44,7 +50,7 @@ class LatentAttention(Mixer):
     supports_append = True
 
     def __init__(self, prefix, hidden, heads, dim, rot_dim, value_dim, kv_rank, q_rank, position, scale, eps,
-                 output_gate=True, out_dtype=None):
+                 output_gate=True, out_dtype=None, shares_latents=False):
         if min(heads, dim, value_dim, kv_rank, q_rank) < 1 or rot_dim < 0:
             raise ValueError("LatentAttention: sizes must be positive")
         if getattr(position, "dims", 0) and position.pairing != "interleaved":
@@ -54,9 +60,15 @@ class LatentAttention(Mixer):
         self.kv_rank, self.q_rank = kv_rank, q_rank
         self.position, self.scale, self.eps = position, float(scale), float(eps)
         self.output_gate = bool(output_gate)
+        self.shares_latents = bool(shares_latents)
+        self.magnitude = float(getattr(position, "magnitude", 1.0))
         self.out_dtype = {None: None, "float32": torch.float32}[out_dtype]
         self.entry = kernels.latent_entry_size(kv_rank, rot_dim)
-        names, rows = [prefix + "dq", prefix + "dkv"], [q_rank, kv_rank + rot_dim]
+        names, rows = [prefix + "dq"], [q_rank]
+        if not self.shares_latents:
+            names.append(prefix + "dkv")
+            rows.append(kv_rank + rot_dim)
+        self.gate_off = sum(rows)                       # where the gate logits begin in the packed product's rows
         if self.output_gate:
             names.append(prefix + "g")
             rows.append(heads)
@@ -76,14 +88,15 @@ class LatentAttention(Mixer):
 
     def tensor_specs(self):
         p = self.prefix
-        return [TensorSpec(p + "dq.norm", (self.q_rank,), "norm"), TensorSpec(p + "dkv.norm", (self.kv_rank,), "norm"),
+        own = [] if self.shares_latents else [TensorSpec(p + "dkv.norm", (self.kv_rank,), "norm")]
+        return [TensorSpec(p + "dq.norm", (self.q_rank,), "norm")] + own + [
                 TensorSpec(p + "uk", (self.heads * self.dim, self.kv_rank)),
                 TensorSpec(p + "uv", (self.heads * self.value_dim, self.kv_rank))]
 
     def bind(self, tensors, rt):
         p, H = self.prefix, self.heads
         self.wq_norm = tensors[p + "dq.norm"].to(torch.float32).contiguous()
-        self.wkv_norm = tensors[p + "dkv.norm"].to(torch.float32).contiguous()
+        self.wkv_norm = None if self.shares_latents else tensors[p + "dkv.norm"].to(torch.float32).contiguous()
         # W_uk^T per head [H, kv_rank, dim]: the query side's product; W_uv per head [H, value_dim, kv_rank]
         self.w_uk_t = tensors[p + "uk"].view(H, self.dim, self.kv_rank).transpose(1, 2).contiguous()
         self.w_uv = tensors[p + "uv"].view(H, self.value_dim, self.kv_rank).contiguous()
@@ -96,31 +109,44 @@ class LatentAttention(Mixer):
         self.rate = rate
         # [W_uk; W_uv] as stored, [H dim + H value_dim, kv_rank]: the expanded prompt form's product
         self.w_kvu = torch.cat([tensors[p + "uk"], tensors[p + "uv"]], 0).contiguous()
-        self._bound = [self.wq_norm, self.wkv_norm, self.w_uk_t, self.w_uv, self.w_kvu]
+        self._bound = [t for t in (self.wq_norm, self.wkv_norm, self.w_uk_t, self.w_uv, self.w_kvu) if t is not None]
 
     def state_spec(self):
-        return KVStateSpec(1, self.entry, 0, planes=1)
+        return None if self.shares_latents else KVStateSpec(1, self.entry, 0, planes=1)
 
     def forward(self, rt, batch, x, state):
         H, D, R, DV, KR, QR = self.heads, self.dim, self.rot_dim, self.value_dim, self.kv_rank, self.q_rank
         T, dev = batch.T, x.device
+        if self.shares_latents != (not state.owned):
+            raise ValueError("a layer that shares latents must be given another layer's state unit by the plan "
+                             "(owns_state=False), and only such a layer")
+        if tuple(state.pool.shape[-2:]) != (kernels.PAGE_TOKENS, self.entry):
+            raise ValueError("the state unit's entries are not of this layer's latent size")
         pool, ptab = state.pool, state.ptab
-        proj = self.down.apply(rt, x)                                   # [T, QR + KR + R (+ H)]
+        G0, mag = self.gate_off, self.magnitude
+        proj = self.down.apply(rt, x)                                   # [T, QR (+ KR + R) (+ H)]
         cq = torch.empty((T, QR), dtype=x.dtype, device=dev)
         HD = self.expand_head
         expand = (batch.kind == "prefill" and HD > 0 and x.dtype == torch.bfloat16 and rt.tensor_core_prompts
                   and batch.max_len >= self.expand_min_tokens and KR % 8 == 0)
-        entries = torch.empty((T, self.entry), dtype=x.dtype, device=dev) if expand else None
+        if expand and self.shares_latents:
+            entries = batch.shared.get(("latent_entries", state.unit))
+            expand = entries is not None
+        else:
+            entries = torch.empty((T, self.entry), dtype=x.dtype, device=dev) if expand else None
+            if expand:
+                batch.shared[("latent_entries", state.unit)] = entries      # for the layers that read this one's latents
         kernels.latent_prepare(cq, proj, 0, QR, self.wq_norm, self.wkv_norm, self.rate, pool, ptab, batch, H, D, R, KR, QR,
-                               self.eps, entries=entries)
+                               self.eps, entries=None if self.shares_latents else entries, mag=mag,
+                               make_entry=not self.shares_latents)
         q = self.up_q.apply(rt, cq)                                      # [T, H (D + R)]
         if expand:
             kvu = rt.linear(entries[:, :KR], self.w_kvu)                 # [T, H D + H DV]
             qkv = torch.empty((T, 3 * H * HD), dtype=x.dtype, device=dev)
-            kernels.latent_expand(qkv, q, kvu, entries, self.rate, pool, ptab, batch, H, D, R, DV, KR, HD)
+            kernels.latent_expand(qkv, q, kvu, entries, self.rate, pool, ptab, batch, H, D, R, DV, KR, HD, mag=mag)
             wide = torch.empty((T, H * HD), dtype=x.dtype, device=dev)
             rt.attention_prefill(wide, qkv[:, :H * HD], qkv[:, H * HD:2 * H * HD], qkv[:, 2 * H * HD:],
-                                 proj[:, QR + KR + R:] if self.output_gate else None, batch, H, H, HD, 0, self.scale)
+                                 proj[:, G0:] if self.output_gate else None, batch, H, H, HD, 0, self.scale)
             if HD == DV:
                 ctx = wide
             else:
@@ -131,7 +157,7 @@ class LatentAttention(Mixer):
         qa = torch.empty((T, H * (KR + R)), dtype=torch.float32, device=dev)
         kernels.head_linear(qa, q, self.w_uk_t, H, D + R, KR + R)
         if R:
-            kernels.latent_query_turn(qa, q, self.rate, pool, ptab, batch, H, D, R, KR)
+            kernels.latent_query_turn(qa, q, self.rate, pool, ptab, batch, H, D, R, KR, mag=mag)
         sums = torch.empty((T, H * KR), dtype=torch.float32, device=dev)
         splits, chunk, parts = 1, 0, None
         # one token per sequence over a bfloat16 cache: the heads are the rows of tensor-core products
@@ -143,7 +169,7 @@ class LatentAttention(Mixer):
             splits, chunk = kernels.latent_attn_splits(T, H, keys, heads_per_block=16 if mma else 32, kv_rank=KR)
             if splits > 1:
                 parts = rt.scratch("latent_attn_parts", T * H * splits * (2 + KR))
-        kernels.latent_attn(sums, qa, proj[:, QR + KR + R:] if self.output_gate else None, pool, ptab, batch, H, R, KR,
+        kernels.latent_attn(sums, qa, proj[:, G0:] if self.output_gate else None, pool, ptab, batch, H, R, KR,
                             self.scale, splits=splits, chunk=chunk, parts=parts, tensor_cores=mma)
         ctx = torch.empty((T, H * DV), dtype=x.dtype, device=dev)
         kernels.head_linear(ctx, sums, self.w_uv, H, KR, DV)

@@ -16,7 +16,11 @@ for the choice only; the weights are the scores without it); `groups` and `keep`
 groups of neighbours, a group's score is its largest choice score, and only members of the best `keep` groups can be
 chosen); `identity` (the last `identity` router outputs stand for experts without matrices whose output is their input
 times the weight; they take part in scores, groups and choice like any other); `scale` (a factor on the weights) and
-`renorm_eps` (added to the sum that `renormalize` divides by).
+`renorm_eps` (added to the sum that `renormalize` divides by); `group_best` (a group's score is the sum of that many of its
+largest choice scores instead of the largest alone).
+
+`activation` "clamped_swish" with `limit` L is an expert of another form: g = min(W_gate x, L), u = clamp(W_up x, -L, L),
+a = g sigmoid(1.702 g) (u + 1).
 """
 from __future__ import annotations
 
@@ -33,15 +37,18 @@ class RoutedSwiGLU(FeedForward):
 
     def __init__(self, prefix, hidden, intermediate, experts, top, gate="sigmoid", renormalize=False,
                  weight_on="input", activation="silu", expert_name="e{}.", correction_name=None, groups=0, keep=0,
-                 identity=0, scale=1.0, renorm_eps=0.0):
-        if gate not in ("sigmoid", "softmax") or weight_on not in ("input", "output") or activation not in ("silu", "gelu_tanh"):
-            raise ValueError("RoutedSwiGLU: gate sigmoid|softmax, weight_on input|output, activation silu|gelu_tanh")
+                 identity=0, scale=1.0, renorm_eps=0.0, group_best=1, limit=0.0):
+        if gate not in ("sigmoid", "softmax") or weight_on not in ("input", "output") or activation not in kernels.ACTIVATIONS:
+            raise ValueError("RoutedSwiGLU: gate sigmoid|softmax, weight_on input|output, activation silu|gelu_tanh|clamped_swish")
+        if activation == "clamped_swish" and not limit > 0.0:
+            raise ValueError("RoutedSwiGLU: the clamped gate needs its limit")
         if top < 1 or experts < 1:
             raise ValueError(f"RoutedSwiGLU: {top} of {experts} experts")
         self.prefix, self.hidden, self.intermediate = prefix, hidden, intermediate
         self.experts, self.top = experts, top
         self.softmax_gate, self.renormalize = gate == "softmax", bool(renormalize)
         self.weight_on_input, self.gelu = weight_on == "input", activation == "gelu_tanh"
+        self.act, self.limit, self.group_best = kernels.ACTIVATIONS[activation], float(limit), int(group_best or 1)
         self.expert_name = expert_name
         self.correction_name, self.groups, self.keep = correction_name, int(groups or 0), int(keep or 0)
         self.identity, self.scale, self.renorm_eps = int(identity or 0), float(scale), float(renorm_eps)
@@ -107,17 +114,25 @@ class RoutedSwiGLU(FeedForward):
         xs = torch.empty((rows, self.hidden), dtype=x.dtype, device=dev) if tensor_cores else None
         kernels.moe_route(ids, wts, perm, dest, work, x, self.router, batch.tok_seq, top, self.softmax_gate, self.renormalize, tile,
                           xs=xs, apply_weight=self.weight_on_input, correction=self.correction, groups=self.groups,
-                          keep=self.keep, identity=self.identity, scale=self.scale, renorm_eps=self.renorm_eps)
+                          keep=self.keep, identity=self.identity, scale=self.scale, renorm_eps=self.renorm_eps,
+                          group_best=self.group_best)
         a = torch.empty((rows, self.intermediate), dtype=x.dtype, device=dev)
         y = torch.empty((rows, self.hidden), dtype=torch.float32, device=dev)
         if tensor_cores:
             groups = kernels.moe_tile_group(work, P, E, tile)
-            kernels.gemm_tc_grouped(a, xs, self.w_up, groups, swiglu=True, err=rt.error_flag,
-                                    block_n=rt._tile_width(rows, 2 * self.intermediate, widths=(256, 128)))
+            if self.act == kernels.ACT_SILU:
+                kernels.gemm_tc_grouped(a, xs, self.w_up, groups, swiglu=True, err=rt.error_flag,
+                                        block_n=rt._tile_width(rows, 2 * self.intermediate, widths=(256, 128)))
+            else:
+                # a gate that the product's epilogue does not have: the plain grouped product, then the gate on its rows
+                gu = torch.empty((rows, 2 * self.intermediate), dtype=x.dtype, device=dev)
+                kernels.gemm_tc_grouped(gu, xs, self.w_up, groups, err=rt.error_flag,
+                                        block_n=rt._tile_width(rows, 2 * self.intermediate, widths=(256, 128)))
+                kernels.swiglu(a, gu, act=self.act, limit=self.limit)
             kernels.gemm_tc_grouped(y, a, self.w_down, groups, err=rt.error_flag, block_n=128)
         else:
             kernels.moe_grouped(a, x, self.w_up, work, perm, wts, top, max_tiles, up=True,
-                                apply_weight=self.weight_on_input, gelu=self.gelu)
+                                apply_weight=self.weight_on_input, act=self.act, limit=self.limit)
             kernels.moe_grouped(y, a, self.w_down, work, perm, wts, top, max_tiles, up=False,
                                 apply_weight=not self.weight_on_input)
         # the grouped tensor-core product has no weights of its own: on the outputs they ride on the residual sum's pieces

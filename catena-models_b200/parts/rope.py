@@ -79,17 +79,30 @@ class PartialYarnRotary(Position):
 
 class PairedRotary(Position):
     """Rotation of the leading `dims` channels of a vector, channel 2i against channel 2i + 1 (the interleaved layout),
-    pair i at the rate theta^(-2i/dims); the other channels pass unchanged.  The rates are formed in double precision on
-    the host and kept as float32; the kernel forms angle = float(position) * rate."""
+    pair i at the rate f_i = theta^(-2i/dims); the other channels pass unchanged.  With `factor` the rates are rescaled for
+    a longer context than the one trained on, by the same rule as `PartialYarnRotary` (turn(t) = dims ln(original /
+    (2 pi t)) / (2 ln theta), lo = max(floor(turn(fast)), 0), hi = min(ceil(turn(slow)), dims - 1), ramp_i = clamp((i - lo)
+    / max(hi - lo, 0.001), 0, 1), rate f_i / factor * ramp_i + f_i (1 - ramp_i)), and sine and cosine are multiplied by
+    `magnitude` = 0.1 ln(factor) + 1.  The rates are formed in double precision on the host and kept as float32; the
+    kernel forms angle = float(position) * rate."""
     prompt_capturable = True
     supports_append = True
     pairing = "interleaved"
 
-    def __init__(self, dims, theta):
+    def __init__(self, dims, theta, factor=None, original=None, fast=None, slow=None):
+        import math
+
         if dims % 2 or dims < 2:
             raise ValueError(f"{dims} turned channels: an even number is needed")
         self.dims, self.theta = dims, float(theta)
         self.rates = [self.theta ** (-2.0 * i / dims) for i in range(dims // 2)]
+        self.magnitude = 1.0
+        if factor is not None:
+            turn = lambda t: dims * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(self.theta))
+            lo, hi = max(math.floor(turn(fast)), 0), min(math.ceil(turn(slow)), dims - 1)
+            ramp = [min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0) for i in range(dims // 2)]
+            self.rates = [f / factor * r + f * (1.0 - r) for f, r in zip(self.rates, ramp)]
+            self.magnitude = 0.1 * math.log(factor) + 1.0
         self._rate = None
 
     def bind(self, tensors, rt):
