@@ -579,6 +579,29 @@ def maferax_config(size, vocab=VOCAB):
                 layers=layers)
 
 
+def relilix_config(size, vocab=VOCAB):
+    """For `--compare relilix`: eight layers of the Relilix decoder at the same width, heads and feed-forward widths as the
+    Maferax model above: four attention layers behind four taps (the attention's heads of 64 channels over the key/value
+    heads, a window of 1,024 tokens, scores capped at 50, the values taken from the keys) and four latent attention layers
+    of Maferax's sizes with rescaled rotation, the last of which reads the latents of the one before; dense and routed
+    feed-forwards in turn, the routed ones with clamped experts in four groups of which two stay open and a shared expert."""
+    z = COMPARE_SIZES[size]
+    att = lambda mlp: dict(type="attention", mlp=mlp, mixer=dict(
+        heads=z["heads"], kv_heads=z["kv_heads"], dim=z["head"], vdim=z["head"], conv=4, scale=z["head"] ** -0.5, softcap=50.0,
+        mask=dict(size=1024), rot=dict(dims=z["head"] // 2, base=1000000.0)))
+    lat = lambda mlp, kv_from=None: dict(type="latent_attention", mlp=mlp, mixer=dict(
+        heads=z["heads"], dim=z["head"], rot_dim=32, vdim=z["head"], kv_rank=z["width"] // 4, q_rank=3 * z["width"] // 8,
+        scale=(z["head"] + 32) ** -0.5,
+        rot=dict(dims=32, base=1000000.0, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0)),
+        **({} if kv_from is None else dict(kv_from=kv_from))))
+    dense = dict(kind="dense", ff=z["ff"])
+    moe = dict(kind="moe", expert=dict(ff=z["expert_ff"], limit=7.0), shared=dict(ff=z["expert_ff"], limit=7.0),
+               router=dict(experts=z["experts"], top=z["top"], groups=dict(count=4, keep=2)))
+    layers = [att(dense), lat(moe), att(moe), lat(dense), att(dense), lat(moe), att(moe), lat(dense, 5)]
+    return dict(architecture="Relilix", vocab=vocab, width=z["width"], norm=dict(eps=1e-6), embedding=dict(scale=z["width"] ** 0.5),
+                layers=layers)
+
+
 def latent_decode_table(pk, device="cuda:0", cases=((8, 16, 256, 32), (128, 16, 256, 32), (64, 32, 512, 32)), held=2048):
     """`--latent-table`: the single-token latent attention alone, in its tensor-core and its CUDA-core form: `B` sequences
     that hold `held` tokens, `H` heads over latents of `KR` + `R` channels, random bfloat16 entries in pages laid out in
@@ -693,7 +716,8 @@ def _kernel_rows(torch, model, prompt_len, batch, vocab):
 
 def compare_designs(which, sizes, prompt_len, batch, steps, pk, tables):
     """Prefill and decode throughput of a design beside the closest earlier one at equal size, random weights: the
-    Narasun decoder beside an LFM3 decoder, the Fozedra and the Maferax decoder beside the Narasun decoder."""
+    Narasun decoder beside an LFM3 decoder, the Fozedra and the Maferax decoder beside the Narasun decoder, the Relilix
+    decoder beside the Maferax decoder."""
     import torch
 
     from catena_models_b200.api import Model
@@ -707,7 +731,8 @@ def compare_designs(which, sizes, prompt_len, batch, steps, pk, tables):
     for size in sizes:
         pairs = {"narasun": (("Narasun", narasun_config), ("LFM3", lfm3_like_config)),
                  "fozedra": (("Fozedra", fozedra_config), ("Narasun", narasun_config)),
-                 "maferax": (("Maferax", maferax_config), ("Narasun", narasun_config))}[which]
+                 "maferax": (("Maferax", maferax_config), ("Narasun", narasun_config)),
+                 "relilix": (("Relilix", relilix_config), ("Maferax", maferax_config))}[which]
         for name, cfg in ((n, make(size, vocab)) for n, make in pairs):
             model = Model.random(cfg, seed=0, std=0.02, dtype="bfloat16", max_tokens=batch * (prompt_len + 256) + 4096,
                                  max_seqs=batch + 1)
@@ -749,9 +774,10 @@ def main():
                     help="time the prompt-attention kernels alone at 2,048, 4,096 and 16,384 tokens and print the table")
     ap.add_argument("--latent-table", action="store_true",
                     help="instead of the JSON line: time the single-token latent attention alone, tensor-core and CUDA-core form")
-    ap.add_argument("--compare", default=None, choices=["narasun", "fozedra", "maferax"],
+    ap.add_argument("--compare", default=None, choices=["narasun", "fozedra", "maferax", "relilix"],
                     help="instead of the JSON line: prompt and decode throughput of that design beside the closest earlier "
-                         "one at equal size (random weights: Narasun beside LFM3, Fozedra and Maferax beside Narasun), as a table")
+                         "one at equal size (random weights: Narasun beside LFM3, Fozedra and Maferax beside Narasun, Relilix beside "
+                         "Maferax), as a table")
     ap.add_argument("--compare-sizes", default="1024,2048", help="widths of `--compare`")
     ap.add_argument("--compare-kernels", action="store_true", help="with `--compare`: also each model's kernel tables")
     ap.add_argument("--print-config", action="store_true",

@@ -22,7 +22,8 @@ namespace cg = cooperative_groups;
 #define SK_MODE_PLAIN 0
 #define SK_MODE_SWIGLU 1
 #define SK_MODE_GEGLU 3                      // as SWIGLU with the tanh form of gelu on the gate
-#define SK_GATED(M) ((M) == SK_MODE_SWIGLU || (M) == SK_MODE_GEGLU)
+#define SK_MODE_CLAMPED 4                    // both halves clamped at a limit L: min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1)
+#define SK_GATED(M) ((M) == SK_MODE_SWIGLU || (M) == SK_MODE_GEGLU || (M) == SK_MODE_CLAMPED)
 #define SK_MODE_PARTS 2          // float partial sums per k-slice, no exchange between the blocks of a row tile
 
 __device__ __forceinline__ void mma_bf16_16816(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -104,7 +105,7 @@ __device__ __forceinline__ void skinny_stream(float (&acc)[NT][4], const bf16* _
 template <int NT, typename TY, int MODE, int UNROLL>
 __global__ void __launch_bounds__(SK_WARPS * 32, NT <= 2 ? 4 : 2)
 gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* __restrict__ W, int M, int N,
-                   int K, long long ldx, long long ldw, long long ldy, long long part_stride) {
+                   int K, long long ldx, long long ldw, long long ldy, long long part_stride, float gate_limit) {
     __shared__ float red[SK_WARPS][NT][32][4];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -180,6 +181,10 @@ gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* _
                 const float gr = rounded<TY>(tot[0]), ur = rounded<TY>(tot[HALVES - 1]);
                 float th = 0.f;      // the hardware's tanh, as in the tensor-core products' epilogue: the same digits from every product
                 if (MODE == SK_MODE_GEGLU) asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.7978845608028654f * (gr + 0.044715f * gr * gr * gr)));
+                if (MODE == SK_MODE_CLAMPED) {
+                    Y[(long long)m * ldy + row] = from_f32<TY>(gated_act(gr, ur, CM_ACT_CLAMPED_SWISH, gate_limit));
+                    continue;
+                }
                 const float ag = MODE == SK_MODE_GEGLU ? 0.5f * gr * (1.f + th) : gr * sigmoid_f32(gr);
                 Y[(long long)m * ldy + row] = from_f32<TY>(ag * ur);
             } else {
@@ -197,7 +202,7 @@ gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* _
 
 template <int NT, typename TY, int MODE>
 static int launch_skinny(void* Y, const void* X, const void* W, int M, int N, int K, long long ldx, long long ldw,
-                         long long ldy, cudaStream_t st) {
+                         long long ldy, cudaStream_t st, float gate_limit = 0.f) {
     const int tiles = (N + 15) / 16;
     // Few row tiles with long rows leave most SMs idle: split K over a cluster of 4 blocks then.
     // (Measured on B200: 2048 x 8192 goes from 15.3 to 10.2 us; with K = 2048 the cluster's
@@ -207,7 +212,7 @@ static int launch_skinny(void* Y, const void* X, const void* W, int M, int N, in
     // goes from 8.6 to 6.7 us against four k-blocks per step at two blocks per SM).
     constexpr int UNROLL = 2;
     cm_launch_cluster(gemm_skinny_kernel<NT, TY, MODE, UNROLL>, dim3(tiles, ksplit), SK_WARPS * 32, 0, st, ksplit, false,
-                      (TY*)Y, (const bf16*)X, (const bf16*)W, M, N, K, ldx, ldw, ldy, 0LL);
+                      (TY*)Y, (const bf16*)X, (const bf16*)W, M, N, K, ldx, ldw, ldy, 0LL, gate_limit);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
@@ -217,19 +222,19 @@ static int launch_skinny_parts(float* P, const void* X, const void* W, int M, in
                                long long ldp, long long part_stride, int ksplit, cudaStream_t st) {
     const int tiles = (N + 15) / 16;
     cm_launch_cluster(gemm_skinny_kernel<NT, float, SK_MODE_PARTS, 2>, dim3(tiles, ksplit), SK_WARPS * 32, 0, st, 1, false, P,
-                      (const bf16*)X, (const bf16*)W, M, N, K, ldx, ldw, ldp, part_stride);
+                      (const bf16*)X, (const bf16*)W, M, N, K, ldx, ldw, ldp, part_stride, 0.f);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
 
 template <typename TY, int MODE>
 static int dispatch_skinny(void* Y, const void* X, const void* W, int M, int N, int K, long long ldx, long long ldw,
-                           long long ldy, cudaStream_t st) {
-    if (M <= 8) return launch_skinny<1, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
-    if (M <= 16) return launch_skinny<2, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
-    if (M <= 32) return launch_skinny<4, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
+                           long long ldy, cudaStream_t st, float gate_limit = 0.f) {
+    if (M <= 8) return launch_skinny<1, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st, gate_limit);
+    if (M <= 16) return launch_skinny<2, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st, gate_limit);
+    if (M <= 32) return launch_skinny<4, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st, gate_limit);
     static_assert(CM_SKINNY_MAX_ROWS == 64, "cm_limits.h: CM_SKINNY_MAX_ROWS");
-    if (M <= CM_SKINNY_MAX_ROWS) return launch_skinny<8, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
+    if (M <= CM_SKINNY_MAX_ROWS) return launch_skinny<8, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st, gate_limit);
     CM_REFUSE("gemm_skinny: %d rows (at most %d)", M, CM_SKINNY_MAX_ROWS);
 }
 
@@ -367,7 +372,7 @@ extern "C" int cm_gemm_skinny_shortconv(void* Y, const void* X, const void* W, c
 // X and W bfloat16; Y bfloat16 (dty = DT_BF16) or float (DT_F32).  swiglu: W has 2N rows
 // ([gate; up]) and Y is [M, N].  K, ldx and ldw must be multiples of 8 (16-byte loads).
 extern "C" int cm_gemm_skinny(int dty, void* Y, const void* X, const void* W, int M, int N, int K, long long ldx,
-                              long long ldw, long long ldy, int swiglu, cudaStream_t st) {
+                              long long ldw, long long ldy, int swiglu, float gate_limit, cudaStream_t st) {
     if (M <= 0 || N <= 0) return CM_OK;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8)
         CM_REFUSE("gemm_skinny: inner size %d and row strides %lld, %lld must be multiples of 8", K, ldx, ldw);
@@ -376,6 +381,10 @@ extern "C" int cm_gemm_skinny(int dty, void* Y, const void* X, const void* W, in
     if (swiglu) {
         if (dty != DT_BF16) return CM_ERR_DTYPE;
         if (swiglu == 2) return dispatch_skinny<bf16, SK_MODE_GEGLU>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
+        if (swiglu == 3) {
+            if (!(gate_limit > 0.f)) CM_REFUSE("gemm_skinny: the clamped gate needs a positive limit");
+            return dispatch_skinny<bf16, SK_MODE_CLAMPED>(Y, X, W, M, N, K, ldx, ldw, ldy, st, gate_limit);
+        }
         return dispatch_skinny<bf16, SK_MODE_SWIGLU>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
     }
     if (dty == DT_BF16) return dispatch_skinny<bf16, SK_MODE_PLAIN>(Y, X, W, M, N, K, ldx, ldw, ldy, st);

@@ -35,6 +35,7 @@ static_assert(TC_BM == CM_FEW_ROWS_MAX_ROWS, "cm_limits.h: CM_FEW_ROWS_MAX_ROWS"
 #define TC_MODE_PLAIN 0
 #define TC_MODE_SWIGLU 1
 #define TC_MODE_GEGLU 2                      // as SWIGLU with the tanh form of gelu on the gate
+#define TC_MODE_CLAMPED 3                    // both halves clamped at a limit L: min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1)
 #define TC_GATED(M) ((M) != TC_MODE_PLAIN)
 
 // What the gate passes through before it meets the up half.
@@ -47,6 +48,17 @@ __device__ __forceinline__ float tc_gate(float g) {
         return 0.5f * g * (1.f + th);
     }
     return __fdividef(g, 1.f + __expf(-g));
+}
+
+// The gated epilogue's output from the gate half g and the up half u.
+template <int MODE>
+__device__ __forceinline__ float tc_gated(float g, float u, float limit) {
+    if (MODE == TC_MODE_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return __fdividef(g, 1.f + __expf(-1.702f * g)) * (u + 1.f);
+    }
+    return tc_gate<MODE>(g) * u;
 }
 
 template <typename TC>
@@ -104,7 +116,7 @@ __global__ void __launch_bounds__(TCP_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, int tma_store_ok, TC* __restrict__ C, int M, int N, int K,
                long long ldc, int ksplit, long long part_stride, int* err, const int* __restrict__ tile_group,
-               int group_rows) {
+               int group_rows, float gate_limit) {
     // tile_group (or null): B is a stack of matrices of group_rows rows each, and the 128 rows of row tile t are
     // multiplied by matrix tile_group[t] (a grouped product: the rows of a routed feed-forward, sorted by expert)
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
@@ -260,7 +272,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                             for (int i = 0; i < 32; ++i) {
                                 const float g = rounded<TC>(v[i]), uu = rounded<TC>(u[i]);
-                                v[i] = tc_gate<MODE>(g) * uu;
+                                v[i] = tc_gated<MODE>(g, uu, gate_limit);
                             }
                         }
                         if (tma_store) {
@@ -341,7 +353,7 @@ template <typename TC, int MODE, int A_ROWS, int TCS_STAGES>
 __global__ void __launch_bounds__(TC_THREADS, 2)
 gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       TC* __restrict__ C, float* __restrict__ parts, long long part_stride, int M, int N, int K,
-                      long long ldc, int splits, int* err) {
+                      long long ldc, int splits, int* err, float gate_limit) {
     constexpr uint32_t A_BYTES = A_ROWS * TC_BK * 2;
     constexpr uint32_t B_BYTES = TCS_BN * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -534,7 +546,7 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 for (int i = 0; i < 4; ++i) {
                     const float u = rounded<TC>(__shfl_down_sync(0xffffffffu, o[i], 16));
                     const float g = rounded<TC>(o[i]);
-                    o[i] = tc_gate<MODE>(g) * u;
+                    o[i] = tc_gated<MODE>(g, u, gate_limit);
                 }
                 if (lane >= 16) continue;
             }
@@ -602,7 +614,7 @@ static int make_map_c(CUtensorMap* map, void* base, long long M, long long N, lo
 template <int BLOCK_N, int STAGES, typename TC, int MODE>
 static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
                      long long ldc, int* err, cudaStream_t st, int ksplit = 1, long long part_stride = 0,
-                     const int* tile_group = nullptr, int groups = 1) {
+                     const int* tile_group = nullptr, int groups = 1, float gate_limit = 0.f) {
     CUtensorMap map_a, map_b;
     const int group_rows = TC_GATED(MODE) ? 2 * N : N;
     const long long b_rows = (long long)groups * group_rows;
@@ -642,7 +654,7 @@ static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K,
     const int num_items = num_tiles * ksplit;
     dim3 grid(num_items < sm_count ? num_items : sm_count);
     cm_launch(kernel, grid, TCP_THREADS, smem, st, map_a, map_b, map_c, tma_store, (TC*)C, M, N, K, ldc, ksplit,
-              part_stride, err, tile_group, group_rows);
+              part_stride, err, tile_group, group_rows, gate_limit);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
@@ -677,7 +689,7 @@ static int splitk_active_clusters(int splits, size_t smem) {
 template <typename TC, int MODE, int A_ROWS, int STAGES>
 static int launch_splitk_rows(void* C, const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
                          long long ldc, int force_splits, int* err, cudaStream_t st, float* parts = nullptr,
-                         long long part_stride = 0) {
+                         long long part_stride = 0, float gate_limit = 0.f) {
     constexpr int OUT_COLS = TC_GATED(MODE) ? TCS_BN / 2 : TCS_BN;
     const size_t smem = (size_t)STAGES * (A_ROWS * TC_BK * 2 + TCS_BN * TC_BK * 2) + 1024;
     auto kernel = gemm_tc_splitk_kernel<TC, MODE, A_ROWS, STAGES>;
@@ -734,7 +746,7 @@ static int launch_splitk_rows(void* C, const void* A, const void* B, int M, int 
     if (rc != CM_OK) return rc;
     // with `parts` the k-slices are independent blocks (no cluster): each leaves its sums in parts[slice]
     cm_launch_cluster(kernel, dim3(n_tiles, splits), TC_THREADS, smem, st, parts ? 1 : splits, true, map_a, map_b, (TC*)C,
-                      parts, part_stride, M, N, K, ldc, splits, err);
+                      parts, part_stride, M, N, K, ldc, splits, err, gate_limit);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
@@ -745,7 +757,7 @@ static int launch_splitk_rows(void* C, const void* A, const void* B, int M, int 
 // many tiles, for products with few rows where the number of tiles decides how many SMs stream
 // weights) or 192 (plain bfloat16 products whose tiles then fill their rounds over the SMs better).  err: device int, raised by a block whose pipeline wait ran out; may be null.
 extern "C" int cm_gemm_tc(int dtc, void* C, const void* A, const void* B, int M, int N, int K, long long lda,
-                          long long ldb, long long ldc, int swiglu, int block_n, int* err, cudaStream_t st) {
+                          long long ldb, long long ldc, int swiglu, int block_n, int* err, float gate_limit, cudaStream_t st) {
     if (M <= 0 || N <= 0) return CM_OK;
     if (K <= 0 || K % 8 || lda % 8 || ldb % 8)
         CM_REFUSE("gemm_tc: inner size %d and row pitches %lld, %lld must be multiples of 8", K, lda, ldb);
@@ -758,6 +770,12 @@ extern "C" int cm_gemm_tc(int dtc, void* C, const void* A, const void* B, int M,
         if (swiglu == 2) {
             if (block_n == 256) return launch_tc<256, 4, bf16, TC_MODE_GEGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
             return launch_tc<128, 6, bf16, TC_MODE_GEGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
+        }
+        if (swiglu == 3) {
+            if (!(gate_limit > 0.f)) CM_REFUSE("gemm_tc: the clamped gate needs a positive limit");
+            if (block_n == 256)
+                return launch_tc<256, 4, bf16, TC_MODE_CLAMPED>(C, A, B, M, N, K, lda, ldb, ldc, err, st, 1, 0, nullptr, 1, gate_limit);
+            return launch_tc<128, 6, bf16, TC_MODE_CLAMPED>(C, A, B, M, N, K, lda, ldb, ldc, err, st, 1, 0, nullptr, 1, gate_limit);
         }
         if (block_n == 256) return launch_tc<256, 4, bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
         return launch_tc<128, 6, bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
@@ -776,7 +794,7 @@ extern "C" int cm_gemm_tc(int dtc, void* C, const void* A, const void* B, int M,
 // cm_gemm_tc; C bfloat16, or float for the plain product.
 extern "C" int cm_gemm_tc_grouped(int dtc, void* C, const void* A, const void* B, int M, int N, int K, long long lda,
                                   long long ldb, long long ldc, int swiglu, int block_n, const int* tile_group, int groups,
-                                  int* err, cudaStream_t st) {
+                                  int* err, float gate_limit, cudaStream_t st) {
     if (M <= 0 || N <= 0) return CM_OK;
     if (K <= 0 || K % 8 || lda % 8 || ldb % 8)
         CM_REFUSE("gemm_tc_grouped: inner size %d and row pitches %lld, %lld must be multiples of 8", K, lda, ldb);
@@ -784,7 +802,14 @@ extern "C" int cm_gemm_tc_grouped(int dtc, void* C, const void* A, const void* B
         CM_REFUSE("gemm_tc_grouped: operands must be 16-byte aligned");
     if (!tile_group || groups < 1) CM_REFUSE("gemm_tc_grouped: the row tiles' groups are missing");
     if (block_n != 128 && block_n != 256) CM_REFUSE("gemm_tc_grouped: tile width %d (128 or 256)", block_n);
-    if (swiglu == 2) CM_REFUSE("gemm_tc_grouped: the gated form has silu only");
+    if (swiglu == 2) CM_REFUSE("gemm_tc_grouped: the gated form has silu and the clamped gate only");
+    if (swiglu == 3) {
+        if (dtc != DT_BF16) return CM_ERR_DTYPE;
+        if (!(gate_limit > 0.f)) CM_REFUSE("gemm_tc_grouped: the clamped gate needs a positive limit");
+        if (block_n == 256)
+            return launch_tc<256, 4, bf16, TC_MODE_CLAMPED>(C, A, B, M, N, K, lda, ldb, ldc, err, st, 1, 0, tile_group, groups, gate_limit);
+        return launch_tc<128, 6, bf16, TC_MODE_CLAMPED>(C, A, B, M, N, K, lda, ldb, ldc, err, st, 1, 0, tile_group, groups, gate_limit);
+    }
     if (swiglu) {
         if (dtc != DT_BF16) return CM_ERR_DTYPE;
         if (block_n == 256)
@@ -825,10 +850,10 @@ extern "C" int cm_gemm_tc_parts(float* P, const void* A, const void* B, int M, i
 template <typename TC, int MODE>
 static int launch_splitk(void* C, const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
                          long long ldc, int force_splits, int* err, cudaStream_t st, float* parts = nullptr,
-                         long long part_stride = 0) {
+                         long long part_stride = 0, float gate_limit = 0.f) {
     if (M <= 64)
-        return launch_splitk_rows<TC, MODE, 64, 4>(C, A, B, M, N, K, lda, ldb, ldc, force_splits, err, st, parts, part_stride);
-    return launch_splitk_rows<TC, MODE, 128, 3>(C, A, B, M, N, K, lda, ldb, ldc, force_splits, err, st, parts, part_stride);
+        return launch_splitk_rows<TC, MODE, 64, 4>(C, A, B, M, N, K, lda, ldb, ldc, force_splits, err, st, parts, part_stride, gate_limit);
+    return launch_splitk_rows<TC, MODE, 128, 3>(C, A, B, M, N, K, lda, ldb, ldc, force_splits, err, st, parts, part_stride, gate_limit);
 }
 
 // The same product for at most 128 rows, with K split over a thread-block cluster when the
@@ -853,7 +878,7 @@ extern "C" int cm_gemm_tc_few_rows_parts(float* P, const void* A, const void* B,
 
 extern "C" int cm_gemm_tc_few_rows(int dtc, void* C, const void* A, const void* B, int M, int N, int K,
                                    long long lda, long long ldb, long long ldc, int swiglu, int splits, int* err,
-                                   cudaStream_t st) {
+                                   float gate_limit, cudaStream_t st) {
     if (M <= 0 || N <= 0) return CM_OK;
     if (M > TC_BM) CM_REFUSE("gemm_tc_few_rows: %d rows (at most %d)", M, TC_BM);
     if (splits < 0 || splits > 8) CM_REFUSE("gemm_tc_few_rows: %d splits (0 to 8)", splits);
@@ -864,8 +889,10 @@ extern "C" int cm_gemm_tc_few_rows(int dtc, void* C, const void* A, const void* 
     int rc;
     if (swiglu) {
         if (dtc != DT_BF16) return CM_ERR_DTYPE;
-        rc = swiglu == 2 ? launch_splitk<bf16, TC_MODE_GEGLU>(C, A, B, M, N, K, lda, ldb, ldc, splits, err, st)
-                         : launch_splitk<bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, splits, err, st);
+        if (swiglu == 3 && !(gate_limit > 0.f)) CM_REFUSE("gemm_tc_few_rows: the clamped gate needs a positive limit");
+        rc = swiglu == 3 ? launch_splitk<bf16, TC_MODE_CLAMPED>(C, A, B, M, N, K, lda, ldb, ldc, splits, err, st, nullptr, 0, gate_limit)
+             : swiglu == 2 ? launch_splitk<bf16, TC_MODE_GEGLU>(C, A, B, M, N, K, lda, ldb, ldc, splits, err, st)
+                           : launch_splitk<bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, splits, err, st);
     } else if (dtc == DT_BF16) {
         rc = launch_splitk<bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, splits, err, st);
     } else if (dtc == DT_F32) {
@@ -884,5 +911,5 @@ extern "C" int cm_gemm_tc_few_rows(int dtc, void* C, const void* A, const void* 
     const int out_cols = swiglu ? 64 : 128;
     const int tiles = (N + out_cols - 1) / out_cols;
     const int width = (dtc == DT_BF16 && sm_count > 0 && tiles > sm_count && tiles <= 2 * sm_count) ? 256 : 128;
-    return cm_gemm_tc(dtc, C, A, B, M, N, K, lda, ldb, ldc, swiglu, width, err, st);
+    return cm_gemm_tc(dtc, C, A, B, M, N, K, lda, ldb, ldc, swiglu, width, err, gate_limit, st);
 }

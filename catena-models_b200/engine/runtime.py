@@ -264,14 +264,10 @@ class Runtime:
     def gate_up_swiglu(self, x, w_gate_up, F, gelu=False, limit=None):
         """a = act(x Wgate^T) * (x Wup^T) for the row-packed [Wgate; Wup]; act is silu, or with `gelu` the tanh form of
         gelu.  The tensor-core and the streaming products apply it in their epilogues.  `limit` = L: the clamped gate
-        instead, a = g' sigmoid(1.702 g') (u' + 1) with g' = min(g, L), u' = clamp(u, -L, L), applied to the plain
-        product's rows by a kernel of its own."""
+        instead, a = g' sigmoid(1.702 g') (u' + 1) with g' = min(g, L), u' = clamp(u, -L, L)."""
         a = torch.empty((x.shape[0], F), dtype=x.dtype, device=x.device)
-        if limit is not None:
-            gu = self.linear(x, w_gate_up)
-            kernels.swiglu(a, gu, act=kernels.ACT_CLAMPED_SWISH, limit=limit)
-            return a
-        flag = 2 if gelu else True
+        flag = 3 if limit is not None else (2 if gelu else True)
+        limit = float(limit or 0.0)
         kind = self._product_kernel(x, w_gate_up)
         # From 9 rows on the tcgen05 few-rows kernel leads (measured on B200 at 16 rows, us, streaming /
         # few-rows: 21,504 x 2,048 weights 25.5 / 20.2, 16,384 x 2,048 15.6 / 14.2, 9,216 x 1,024 7.7 / 7.4; at 8
@@ -279,18 +275,18 @@ class Runtime:
         if kind == "skinny" and x.shape[0] > 8 and self._tma_operands(x, w_gate_up):
             kind = "few_rows"
         if kind == "skinny":
-            kernels.gemm_skinny(a, x, w_gate_up, swiglu=flag)
+            kernels.gemm_skinny(a, x, w_gate_up, swiglu=flag, limit=limit)
             return a
         if kind == "few_rows":
-            kernels.gemm_tc_few_rows(a, x, w_gate_up, swiglu=flag, err=self.error_flag)
+            kernels.gemm_tc_few_rows(a, x, w_gate_up, swiglu=flag, err=self.error_flag, limit=limit)
             return a
         if kind == "tiled":
             # a 256-wide tile of the packed matrix gives 128 output columns
-            kernels.gemm_tc(a, x, w_gate_up, swiglu=flag, err=self.error_flag,
+            kernels.gemm_tc(a, x, w_gate_up, swiglu=flag, err=self.error_flag, limit=limit,
                             block_n=self._tile_width(x.shape[0], 2 * F, widths=(256, 128)))
             return a
         gu = self.linear(x, w_gate_up)
-        kernels.swiglu(a, gu, gelu=gelu)
+        kernels.swiglu(a, gu, act=flag - 1 if flag is not True else 0, limit=limit)
         return a
 
     # ------------------------------------------------------------------ attention

@@ -29,9 +29,9 @@ _SIGNATURES = {
     "cm_swiglu": [_i, _vp, _vp, _i, _i, _i, _f, _vp],
     "cm_gather_rows": [_i, _vp, _vp, _vp, _i, _i, _vp],
     "cm_gemm_simt": [_i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
-    "cm_gemm_skinny": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp],
-    "cm_gemm_tc": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _vp],
-    "cm_gemm_tc_few_rows": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _vp],
+    "cm_gemm_skinny": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _f, _vp],
+    "cm_gemm_tc": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _f, _vp],
+    "cm_gemm_tc_few_rows": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _f, _vp],
     "cm_qk_prepare": [_i, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i,
                       _i, _f, _i, _f, _i, _vp],
     "cm_attn_prefill_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _vp],
@@ -77,7 +77,7 @@ _SIGNATURES = {
     "cm_latent_attn_mma": [_vp, _vp],
     "cm_head_linear": [_i, _vp, _vp, _vp, _ll, _i, _i, _i, _ll, _ll, _i, _i, _i, _i, _vp],
     "cm_moe_gather": [_i, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
-    "cm_gemm_tc_grouped": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _i, _vp, _vp],
+    "cm_gemm_tc_grouped": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _i, _vp, _f, _vp],
     "cm_moe_grouped": [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
 }
 
@@ -444,13 +444,14 @@ def gemm_simt(y, x, w):
            cost=lambda: (f"{M}x{N}x{K}", _nbytes(x, w, y), 2 * M * N * K))
 
 
-_GATE_SUFFIX = ("", "_swiglu", "_geglu")     # a product's name by its gate flag
+_GATE_SUFFIX = ("", "_swiglu", "_geglu", "_clamped")     # a product's name by its gate flag
 
 
-def gemm_skinny(y, x, w, swiglu=False):
+def gemm_skinny(y, x, w, swiglu=False, limit=0.0):
     """y = x @ w^T for at most 64 bfloat16 rows, weights streamed once (mma.sync, float sums).
-    swiglu: w is [gate; up] with 2F rows and y[M, F] = silu(x Wgate^T) * (x Wup^T); swiglu=2 (all three products that
-    take the flag): the tanh form of gelu in silu's place."""
+    swiglu: w is [gate; up] with 2F rows and y[M, F] = silu(x Wgate^T) * (x Wup^T); swiglu=2 (all products that
+    take the flag): the tanh form of gelu in silu's place; swiglu=3 with `limit` L: the clamped gate, g' sigmoid(1.702 g')
+    (u' + 1) with g' = min(g, L), u' = clamp(u, -L, L)."""
     _need_cuda(y, x, w)
     M, K = x.shape
     N = y.shape[1]
@@ -465,7 +466,7 @@ def gemm_skinny(y, x, w, swiglu=False):
                    ldy=y.stride(0), x=_ptr(x), w=_ptr(w), y=_ptr(y))
         return
     _check(lib().cm_gemm_skinny(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0),
-                                y.stride(0), int(swiglu), _stream()), "gemm_skinny" + _GATE_SUFFIX[int(swiglu)],
+                                y.stride(0), int(swiglu), float(limit), _stream()), "gemm_skinny" + _GATE_SUFFIX[int(swiglu)],
            cost=lambda: (f"{M}x{w.shape[0]}x{K}", _nbytes(x, w, y), 2 * M * w.shape[0] * K))
 
 
@@ -520,7 +521,7 @@ def gemm_tc_parts(parts, x, w, err=None, block_n=256):
            cost=lambda: (f"{M}x{N}x{K} in {S} runs", _nbytes(x, w, parts), 2 * M * N * K))
 
 
-def gemm_tc(y, x, w, swiglu=False, err=None, block_n=256):
+def gemm_tc(y, x, w, swiglu=False, err=None, block_n=256, limit=0.0):
     """y = x @ w^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory), any
     number of bfloat16 rows.  swiglu: w is [gate; up] with 2F rows and y[M, F] = silu(g) * u.
     err: device int32 that a block raises if one of its bounded pipeline waits runs out.
@@ -536,11 +537,11 @@ def gemm_tc(y, x, w, swiglu=False, err=None, block_n=256):
     if x.stride(1) != 1 or w.stride(1) != 1 or y.stride(1) != 1:
         raise KernelError("gemm_tc takes row-major operands")
     _check(lib().cm_gemm_tc(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0),
-                            y.stride(0), int(swiglu), block_n, _ptr(err), _stream()), "gemm_tc" + _GATE_SUFFIX[int(swiglu)],
+                            y.stride(0), int(swiglu), block_n, _ptr(err), float(limit), _stream()), "gemm_tc" + _GATE_SUFFIX[int(swiglu)],
            cost=lambda: (f"{M}x{w.shape[0]}x{K}", _nbytes(x, w, y), 2 * M * w.shape[0] * K))
 
 
-def gemm_tc_few_rows(y, x, w, swiglu=False, err=None, splits=0):
+def gemm_tc_few_rows(y, x, w, swiglu=False, err=None, splits=0, limit=0.0):
     """gemm_tc for at most 128 rows.  When the product has too few 128-column tiles for the
     device, K is split over a thread-block cluster of up to 8 blocks that add their partial
     sums through distributed shared memory.  splits: 0 chooses, 1..8 forces."""
@@ -554,7 +555,7 @@ def gemm_tc_few_rows(y, x, w, swiglu=False, err=None, splits=0):
     if x.stride(1) != 1 or w.stride(1) != 1 or y.stride(1) != 1:
         raise KernelError("gemm_tc_few_rows takes row-major operands")
     _check(lib().cm_gemm_tc_few_rows(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0),
-                                     w.stride(0), y.stride(0), int(swiglu), splits, _ptr(err), _stream()),
+                                     w.stride(0), y.stride(0), int(swiglu), splits, _ptr(err), float(limit), _stream()),
            "gemm_tc_few_rows" + _GATE_SUFFIX[int(swiglu)],
            cost=lambda: (f"{M}x{w.shape[0]}x{K}", _nbytes(x, w, y), 2 * M * w.shape[0] * K))
 
@@ -1317,9 +1318,10 @@ def moe_grouped(out, x, w, work, perm, wts, top, max_tiles, up, apply_weight, ge
                          2 * out.shape[0] * w.shape[1] * K))
 
 
-def gemm_tc_grouped(y, x, w, tile_group, swiglu=False, err=None, block_n=256):
+def gemm_tc_grouped(y, x, w, tile_group, swiglu=False, err=None, block_n=256, limit=0.0):
     """`gemm_tc` with a matrix per row tile: w [groups, N (2 N when swiglu), K] bfloat16, tile_group (device int32)
-    names the matrix that multiplies each tile of 128 rows of x.  y bfloat16, or float32 for the plain product."""
+    names the matrix that multiplies each tile of 128 rows of x.  y bfloat16, or float32 for the plain product.
+    swiglu: True (silu) or 3 with `limit` (the clamped gate), as `gemm_tc`."""
     M, K = x.shape
     G, N = w.shape[0], y.shape[1]
     if w.shape[2] != K or w.shape[1] != (2 * N if swiglu else N) or y.shape[0] != M or tile_group.numel() * 128 < M:
@@ -1327,7 +1329,7 @@ def gemm_tc_grouped(y, x, w, tile_group, swiglu=False, err=None, block_n=256):
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not (x.is_contiguous() and w.is_contiguous() and y.is_contiguous()):
         raise KernelError("gemm_tc_grouped takes contiguous bfloat16 operands")
     _check(lib().cm_gemm_tc_grouped(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(1), y.stride(0),
-                                    int(swiglu), block_n, _ptr(tile_group), G, _ptr(err), _stream()),
-           "gemm_tc_grouped" + ("_swiglu" if swiglu else ""),
+                                    int(swiglu), block_n, _ptr(tile_group), G, _ptr(err), float(limit), _stream()),
+           "gemm_tc_grouped" + _GATE_SUFFIX[int(swiglu)],
            cost=lambda: (f"{M}x{w.shape[1]}x{K} over {G} matrices", _nbytes(x, y) + min(G, -(-M // 128)) * w[0].numel() * 2,
                          2 * M * w.shape[1] * K))

@@ -117,7 +117,8 @@ class LatentAttention(Mixer):
     def forward(self, rt, batch, x, state):
         H, D, R, DV, KR, QR = self.heads, self.dim, self.rot_dim, self.value_dim, self.kv_rank, self.q_rank
         T, dev = batch.T, x.device
-        if self.shares_latents != (not state.owned):
+        owned, unit = getattr(state, "owned", True), getattr(state, "unit", -1)
+        if self.shares_latents != (not owned):
             raise ValueError("a layer that shares latents must be given another layer's state unit by the plan "
                              "(owns_state=False), and only such a layer")
         if tuple(state.pool.shape[-2:]) != (kernels.PAGE_TOKENS, self.entry):
@@ -130,12 +131,12 @@ class LatentAttention(Mixer):
         expand = (batch.kind == "prefill" and HD > 0 and x.dtype == torch.bfloat16 and rt.tensor_core_prompts
                   and batch.max_len >= self.expand_min_tokens and KR % 8 == 0)
         if expand and self.shares_latents:
-            entries = batch.shared.get(("latent_entries", state.unit))
+            entries = batch.shared.get(("latent_entries", unit))
             expand = entries is not None
         else:
             entries = torch.empty((T, self.entry), dtype=x.dtype, device=dev) if expand else None
             if expand:
-                batch.shared[("latent_entries", state.unit)] = entries      # for the layers that read this one's latents
+                batch.shared[("latent_entries", unit)] = entries      # for the layers that read this one's latents
         kernels.latent_prepare(cq, proj, 0, QR, self.wq_norm, self.wkv_norm, self.rate, pool, ptab, batch, H, D, R, KR, QR,
                                self.eps, entries=None if self.shares_latents else entries, mag=mag,
                                make_entry=not self.shares_latents)

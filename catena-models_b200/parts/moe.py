@@ -120,15 +120,9 @@ class RoutedSwiGLU(FeedForward):
         y = torch.empty((rows, self.hidden), dtype=torch.float32, device=dev)
         if tensor_cores:
             groups = kernels.moe_tile_group(work, P, E, tile)
-            if self.act == kernels.ACT_SILU:
-                kernels.gemm_tc_grouped(a, xs, self.w_up, groups, swiglu=True, err=rt.error_flag,
-                                        block_n=rt._tile_width(rows, 2 * self.intermediate, widths=(256, 128)))
-            else:
-                # a gate that the product's epilogue does not have: the plain grouped product, then the gate on its rows
-                gu = torch.empty((rows, 2 * self.intermediate), dtype=x.dtype, device=dev)
-                kernels.gemm_tc_grouped(gu, xs, self.w_up, groups, err=rt.error_flag,
-                                        block_n=rt._tile_width(rows, 2 * self.intermediate, widths=(256, 128)))
-                kernels.swiglu(a, gu, act=self.act, limit=self.limit)
+            kernels.gemm_tc_grouped(a, xs, self.w_up, groups, swiglu=3 if self.act == kernels.ACT_CLAMPED_SWISH else True,
+                                    err=rt.error_flag, limit=self.limit,
+                                    block_n=rt._tile_width(rows, 2 * self.intermediate, widths=(256, 128)))
             kernels.gemm_tc_grouped(y, a, self.w_down, groups, err=rt.error_flag, block_n=128)
         else:
             kernels.moe_grouped(a, x, self.w_up, work, perm, wts, top, max_tiles, up=True,

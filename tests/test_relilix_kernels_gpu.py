@@ -324,6 +324,41 @@ def test_clamped_gate_alone(K, dtype, tol):
     assert float((gu[:, :F].double() > limit).double().mean()) > 0.1          # the clamp is at work on this input
 
 
+@pytest.mark.parametrize("kernel, M", [("skinny", 5), ("skinny", 16), ("few_rows", 40), ("few_rows", 128), ("tiled", 300),
+                                       ("tiled256", 700), ("grouped", 384)])
+def test_clamped_gate_in_the_products_epilogues(K, kernel, M):
+    """a = g' sigmoid(1.702 g') (u' + 1) formed where the product [gate; up] leaves its sums: the streaming product, the
+    few-rows and the tiled tcgen05 products, and the grouped one with a matrix per row tile."""
+    F, Kin, limit = 136, 192, 0.8
+    x = rnd(M, Kin, dtype=torch.bfloat16, seed=1)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+
+    def plain_rows(rows, w):
+        gu = rows.double().cpu() @ w.double().cpu().T
+        g = gu[:, :F].to(torch.bfloat16).double().clamp(max=limit)
+        u = gu[:, F:].to(torch.bfloat16).double().clamp(-limit, limit)
+        return g * torch.sigmoid(1.702 * g) * (u + 1.0)
+
+    if kernel == "grouped":
+        w = rnd(3, 2 * F, Kin, dtype=torch.bfloat16, scale=0.12, seed=2)
+        groups = torch.tensor([2, 0, 1], dtype=torch.int32, device=DEV)
+        K.gemm_tc_grouped(out, x, w, groups, swiglu=3, err=err, block_n=128, limit=limit)
+        ref = torch.cat([plain_rows(x[128 * t:128 * (t + 1)], w[int(groups[t])]) for t in range(3)])
+    else:
+        w = rnd(2 * F, Kin, dtype=torch.bfloat16, scale=0.12, seed=2)
+        if kernel == "skinny":
+            K.gemm_skinny(out, x, w, swiglu=3, limit=limit)
+        elif kernel == "few_rows":
+            K.gemm_tc_few_rows(out, x, w, swiglu=3, err=err, limit=limit)
+        else:
+            K.gemm_tc(out, x, w, swiglu=3, err=err, block_n=256 if kernel == "tiled256" else 128, limit=limit)
+        ref = plain_rows(x, w)
+    assert int(err) == 0
+    assert float((out.double().cpu() - ref).abs().max()) < 1.2e-2 * float(ref.abs().max())
+    assert float((ref.abs() > 0.5).double().mean()) > 0.05 and float(ref.max()) <= limit * (limit + 1.0) + 1e-9
+
+
 @pytest.mark.parametrize("dtype, tensor_cores", [("float32", True), ("bfloat16", True), ("bfloat16", False)])
 def test_routed_feed_forward_with_clamped_experts_and_a_shared_one(K, dtype, tensor_cores):
     """The routed part with its grouped products (CUDA cores, and the tcgen05 grouped product with the gate behind it)
