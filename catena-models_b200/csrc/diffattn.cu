@@ -159,6 +159,133 @@ tap_rotate_store_kernel(const TapRotArgs a) {
     }
 }
 
+// Two neighbouring channels as floats, and back: one 4-byte access for bfloat16, one 8-byte access for float.
+__device__ __forceinline__ float2 load_pair(const bf16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+__device__ __forceinline__ float2 load_pair(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ void store_pair(bf16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
+__device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+
+// The interleaved form for long steps: a thread owns the channels c, c + 1 (a rotation pair, so nobody forms a partner's
+// filter a second time) and TP_TOK consecutive rows.  The rows' filter inputs overlap: TP_TOK + K - 1 rows are fetched for
+// TP_TOK results, each as one access for both channels.  Rows of a step lie side by side per sequence, so the input of
+// position s >= p0 of the sequence of row t at position pos is row t - (pos - s); what is older comes from the state (a
+// sequence that stands at p0 > 0) or is zero.
+#define TP_TOK 8
+template <typename T, int K>
+__global__ void __launch_bounds__(TR_THREADS)
+tap_rotate_pairs_kernel(const TapRotArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int C = a.QC + a.KC + a.VC;
+    const int c = 2 * (blockIdx.y * TR_THREADS + threadIdx.x);
+    if (c >= C) return;
+    const int t0 = blockIdx.x * TP_TOK;
+    const int cr = c < a.QC ? c : c - a.QC;
+    const int e = cr % max(a.sub, 1);
+    const bool turned = c < a.QC + a.KC && a.rate && e < a.rot;
+    const float b0 = a.bias ? a.bias[c] : 0.f, b1 = a.bias ? a.bias[c + 1] : 0.f;
+    float w0[K], w1[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+        w0[j] = a.taps[(long long)c * K + j];
+        w1[j] = a.taps[(long long)(c + 1) * K + j];
+    }
+    float2 u[TP_TOK + K - 1];
+#pragma unroll
+    for (int r = 0; r < TP_TOK + K - 1; ++r) {
+        const int row = t0 - (K - 1) + r;
+        u[r] = make_float2(0.f, 0.f);
+        if (row >= 0 && row < a.T) {
+            u[r] = load_pair((const T*)a.proj + (long long)row * a.ldp + c);
+            u[r].x += b0;
+            u[r].y += b1;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TP_TOK; ++i) {
+        const int t = t0 + i;
+        if (t >= a.T) break;
+        const int b = a.tok_seq[t];
+        if (b < 0) continue;
+        const int pos = a.tok_pos[t], p0 = a.seq_pos0[b];
+        float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < K; ++j) {
+            const int s = pos - (K - 1) + j;
+            float x0 = u[i + j].x, x1 = u[i + j].y;
+            if (s < p0) {
+                x0 = x1 = 0.f;
+                if (s >= 0) {
+                    const float* st = a.state + (long long)a.seq_slot[b] * a.state_stride + (long long)(s % K) * C + c;
+                    x0 = st[0];
+                    x1 = st[1];
+                }
+            }
+            y0 = fmaf(w0[j], x0, y0);
+            y1 = fmaf(w1[j], x1, y1);
+        }
+        float v0 = y0, v1 = y1;
+        if (turned) {
+            float sn, cs;
+            sincosf((float)pos * a.rate[e >> 1], &sn, &cs);
+            sn *= a.mag;
+            cs *= a.mag;
+            v0 = y0 * cs - y1 * sn;
+            v1 = y1 * cs + y0 * sn;
+        }
+        if (c < a.QC) {
+            store_pair((T*)a.q_out + (long long)t * a.ldq + c, v0, v1);
+            continue;
+        }
+        if (a.rows_out) {
+            T* o = (T*)a.q_out + (long long)t * a.ldq + a.QC;
+            store_pair(o + cr, v0, v1);
+            if (cr < a.KC && a.value_from_key) store_pair(o + a.KC + cr, y0, y1);
+        }
+        bool keep = !a.no_store;
+        int entry = pos;
+        if (a.ring > 0) {
+            const int end = p0 + a.seq_start[b + 1] - a.seq_start[b];
+            keep = keep && pos >= end - a.ring;
+            entry = pos % a.ring;
+        }
+        if (!keep) continue;
+        const int page = a.ptab[(long long)a.seq_slot[b] * a.ptab_stride + entry / PAGE_TOKENS], row = entry % PAGE_TOKENS;
+        if (cr < a.KC) {
+            const int g = cr / a.KW, off = cr - g * a.KW;
+            store_pair(kv_tile((T*)a.pool, 0, a.pages, page, g, a.G, a.HDC) + (long long)row * a.HDC + off, v0, v1);
+            if (a.value_from_key)
+                store_pair(kv_tile((T*)a.pool, 1, a.pages, page, g, a.G, a.HDC) + (long long)row * a.HDC + off, y0, y1);
+        } else {
+            const int cv = cr - a.KC, g = cv / a.DV, off = cv - g * a.DV;
+            store_pair(kv_tile((T*)a.pool, 1, a.pages, page, g, a.G, a.HDC) + (long long)row * a.HDC + off, v0, v1);
+        }
+    }
+}
+
+// Whether the pairs form can run: interleaved pairs, a long step, and every size and pitch even so that two channels are one
+// access (heads, key and value rows, the entry size, the pitches of the rows in and out; bases aligned to two elements).
+template <typename T>
+static bool tap_pairs_fit(const TapRotArgs& a) {
+    const uintptr_t two = 2 * sizeof(T);
+    if (!a.interleaved || a.one_token_each || a.T < 64 || a.K > 4) return false;
+    if ((a.QC | a.KC | a.VC | a.sub | a.rot | a.KW | a.DV | a.HDC) & 1) return false;
+    if ((a.ldp | a.ldq) & 1) return false;
+    return !(((uintptr_t)a.proj | (uintptr_t)a.q_out | (uintptr_t)a.pool) % two);
+}
+
+template <typename T>
+static void launch_tap_pairs(const TapRotArgs& a, cudaStream_t st) {
+    const int C = a.QC + a.KC + a.VC;
+    dim3 grid((a.T + TP_TOK - 1) / TP_TOK, (C / 2 + TR_THREADS - 1) / TR_THREADS);
+    switch (a.K) {
+    case 1: cm_launch(tap_rotate_pairs_kernel<T, 1>, grid, TR_THREADS, 0, st, a); break;
+    case 2: cm_launch(tap_rotate_pairs_kernel<T, 2>, grid, TR_THREADS, 0, st, a); break;
+    case 3: cm_launch(tap_rotate_pairs_kernel<T, 3>, grid, TR_THREADS, 0, st, a); break;
+    default: cm_launch(tap_rotate_pairs_kernel<T, 4>, grid, TR_THREADS, 0, st, a); break;
+    }
+}
+
 // The state after a step of several tokens: the projected rows of the sequence's last K - 1 positions that the
 // step brought go to their rows of the ring (older ones lie there already).  A launch of its own, behind the
 // outputs: a long step overwrites rows that its first tokens read.
@@ -196,12 +323,14 @@ extern "C" int cm_tap_rotate_store(int dt, const TapRotArgs* args, cudaStream_t 
     const bool many = a.T >= 512 && !a.one_token_each;               // long steps: four tokens a thread
     dim3 grid(many ? (a.T + 3) / 4 : a.T, (C + TR_THREADS - 1) / TR_THREADS), sgrid((C + TR_THREADS - 1) / TR_THREADS, a.B);
     if (dt == DT_F32) {
-        if (many) cm_launch(tap_rotate_store_kernel<float, 4>, grid, TR_THREADS, 0, st, a);
+        if (tap_pairs_fit<float>(a)) launch_tap_pairs<float>(a, st);
+        else if (many) cm_launch(tap_rotate_store_kernel<float, 4>, grid, TR_THREADS, 0, st, a);
         else cm_launch(tap_rotate_store_kernel<float, 1>, grid, TR_THREADS, 0, st, a);
         CM_CHECK_LAUNCH();
         if (!a.one_token_each && a.K > 1) cm_launch(tap_state_kernel<float>, sgrid, TR_THREADS, 0, st, a);
     } else if (dt == DT_BF16) {
-        if (many) cm_launch(tap_rotate_store_kernel<bf16, 4>, grid, TR_THREADS, 0, st, a);
+        if (tap_pairs_fit<bf16>(a)) launch_tap_pairs<bf16>(a, st);
+        else if (many) cm_launch(tap_rotate_store_kernel<bf16, 4>, grid, TR_THREADS, 0, st, a);
         else cm_launch(tap_rotate_store_kernel<bf16, 1>, grid, TR_THREADS, 0, st, a);
         CM_CHECK_LAUNCH();
         if (!a.one_token_each && a.K > 1) cm_launch(tap_state_kernel<bf16>, sgrid, TR_THREADS, 0, st, a);
