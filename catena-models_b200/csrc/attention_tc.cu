@@ -512,8 +512,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     early = ft_mbar_test(o_full + 8 * (g * NP + (T - 2) % NP), (uint32_t)(((T - 2) / NP) & 1));
                 tmem_load_wait();
                 if (past.cap_in > 0.f) {                             // bounded scores: tanh(s scale / cap); cap log2 e is in scale_log2
+                    // a row whose scores all stay within a quarter of the cap takes the series, which needs no special-function
+                    // operation (the softmax keeps that unit busy); any other row (also one with a score that is not a number,
+                    // from rows that are not the sequence's and are masked below) the exponential form
+                    float am4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                    for (int c = 0; c < FT_TILE; ++c) v[c] = tanh_fast(v[c] * past.cap_in);
+                    for (int c = 0; c < FT_TILE; ++c) am4[c & 3] = fmaxf(am4[c & 3], fabsf(v[c]));
+                    const float amax = fmaxf(fmaxf(am4[0], am4[1]), fmaxf(am4[2], am4[3])) * past.cap_in;
+                    if (amax < TANH_SERIES_BOUND) {
+#pragma unroll
+                        for (int c = 0; c < FT_TILE; ++c) v[c] = tanh_series(v[c] * past.cap_in);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < FT_TILE; ++c) v[c] = tanh_fast(v[c] * past.cap_in);
+                    }
                 }
                 // the keys of the tile that this row sees are the columns lo .. hi - 1; all of them: no comparisons needed
                 const int lo = window > 0 ? max(0, row - window + 1 - k0) : 0;

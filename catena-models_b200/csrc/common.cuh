@@ -157,10 +157,18 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // A score bounded to (-cap, cap): cap * tanh(s / cap); cap <= 0 leaves it as it is.
 __device__ __forceinline__ float soft_cap(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
 // tanh from one exponential and one division (absolute error of a few 2^-24: for kernels that form
-// thousands of them per row and round what follows to bfloat16).
+// thousands of them per row and round what follows to bfloat16).  (The reciprocal by Newton steps on the FMA pipe
+// instead of the special-function unit was measured slower in the tcgen05 attention: 106 against 97 us.)
 __device__ __forceinline__ float tanh_fast(float x) {
     const float t = __expf(2.f * fminf(fmaxf(x, -15.f), 15.f));
     return 1.f - __fdividef(2.f, t + 1.f);
+}
+// tanh(x) for |x| < 1/4 by its series up to x^7 (the next term, 62/2835 x^9, is below 9e-8 there): no special-function
+// operation at all.  A cap of tens over scores of a few units keeps whole tiles in this range.
+#define TANH_SERIES_BOUND 0.25f
+__device__ __forceinline__ float tanh_series(float x) {
+    const float x2 = x * x;
+    return x * fmaf(x2, fmaf(x2, fmaf(x2, -17.f / 315.f, 2.f / 15.f), -1.f / 3.f), 1.f);
 }
 __device__ __forceinline__ float sigmoid_f32(float x) { return 1.f / (1.f + expf(-x)); }
 

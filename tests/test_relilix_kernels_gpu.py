@@ -56,13 +56,17 @@ def _views(q, k, v, QH, KVH, HD):
 
 
 # ------------------------------------------------------------------------------------------ whole prompts
+@pytest.mark.parametrize("cap", [2.0, 50.0])
 @pytest.mark.parametrize("impl, dtype, QH, KVH, HD, T, window", [
     ("simt", torch.float32, 4, 2, 24, 150, 37), ("simt", torch.bfloat16, 3, 1, 40, 130, 0), ("simt", torch.float32, 2, 2, 16, 90, 3),
     ("mma", torch.bfloat16, 4, 2, 64, 300, 100), ("mma", torch.bfloat16, 2, 1, 112, 200, 0), ("mma", torch.bfloat16, 6, 6, 16, 140, 64),
     ("tc", torch.bfloat16, 4, 2, 64, 900, 0), ("tc", torch.bfloat16, 2, 1, 128, 1000, 800), ("tc", torch.bfloat16, 2, 2, 64, 700, 130)])
-def test_capped_scores_in_prompt_attention(K, impl, dtype, QH, KVH, HD, T, window):
-    """Random rows whose raw scores reach several times the cap: the result follows the capped scores, not the raw ones."""
-    cap, scale = 2.0, HD ** -0.5
+def test_capped_scores_in_prompt_attention(K, impl, dtype, QH, KVH, HD, T, window, cap):
+    """Random rows whose raw scores reach several times a cap of 2, or a fifth of a cap of 50 (where the tcgen05 kernel forms
+    the tanh of most rows by its series): the result follows the capped scores, not the raw ones."""
+    if cap > 2.0 and impl != "tc":
+        pytest.skip("one form of the tanh")
+    scale = HD ** -0.5
     _, q, k, v = _rows(T, QH, KVH, HD, dtype, 3)
     lens = [T - 70, 70]                                # two sequences side by side
     starts = torch.tensor([0, lens[0], T], dtype=torch.int32, device=DEV)
@@ -78,7 +82,7 @@ def test_capped_scores_in_prompt_attention(K, impl, dtype, QH, KVH, HD, T, windo
     ref = torch.cat([capped_attention(qv[a:b], kv[a:b], vv[a:b], window, scale, cap) for a, b in ((0, lens[0]), (lens[0], T))])
     close(ctx.view(T, QH, HD), ref, dtype)
     raw = torch.cat([capped_attention(qv[a:b], kv[a:b], vv[a:b], window, scale, 0.0) for a, b in ((0, lens[0]), (lens[0], T))])
-    assert float((ref - raw).abs().max()) > 0.2           # the cap matters on this input
+    assert float((ref - raw).abs().max()) > (0.2 if cap == 2.0 else 0.02)           # the cap matters on this input
 
 
 @pytest.mark.parametrize("impl, dtype, HD, T", [("simt", torch.float32, 32, 400), ("mma", torch.bfloat16, 64, 400),
