@@ -204,8 +204,11 @@ class RelilixConfig:
             if f is not None and f.kind == "moe":
                 if f.top > f.experts:
                     problems.append(f"layers[{i}]: top {f.top} of {f.experts} experts")
-                if f.experts > 64:
-                    problems.append(f"layers[{i}]: {f.experts} experts: the router kernel takes up to 64")
+                if f.experts > 4096:
+                    problems.append(f"layers[{i}]: {f.experts} experts: the router kernel takes up to 4096")
+                if f.groups > 64 or (f.groups and f.experts // f.groups > 64):
+                    problems.append(f"layers[{i}]: {f.groups} groups of {f.experts // f.groups} experts: the router kernel takes up to "
+                                    f"64 groups of up to 64")
                 if f.groups and (f.experts % f.groups or not 1 <= f.keep <= f.groups or f.keep * (f.experts // f.groups) < f.top):
                     problems.append(f"layers[{i}]: {f.groups} groups over {f.experts} experts, {f.keep} kept, top {f.top}")
         if problems:
