@@ -45,6 +45,8 @@ struct TapRotArgs {
                                  // step only the last `ring` positions of a sequence are written
     int no_store;                // the cache is left as it is (the caller writes the step's rows later)
     int rows_out;                // q_out rows hold [q | turned k | v] (ldq >= QC + KC + value channels), not the queries alone
+    int from_zero;               // every sequence of the step starts at position 0: nothing reads the filter's state, so the
+                                 // pairs form writes it in the same launch
 };
 
 #define TR_THREADS 128
@@ -174,15 +176,34 @@ __device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinte
 template <typename T, int K>
 __global__ void __launch_bounds__(TR_THREADS)
 tap_rotate_pairs_kernel(const TapRotArgs a) {
+    // what every thread of the block needs to know of the block's rows, looked up once: sequence (-1: padding), position, the
+    // sequence's first position of the step and its end, its slot, and the page of the row's cache entry (-1: not written)
+    __shared__ int r_seq[TP_TOK], r_pos[TP_TOK], r_p0[TP_TOK], r_end[TP_TOK], r_slot[TP_TOK], r_page[TP_TOK];
     pdl_trigger();
     pdl_wait();
     const int C = a.QC + a.KC + a.VC;
     const int c = 2 * (blockIdx.y * TR_THREADS + threadIdx.x);
-    if (c >= C) return;
     const int t0 = blockIdx.x * TP_TOK;
+    if (threadIdx.x < TP_TOK) {
+        const int i = threadIdx.x, t = t0 + i;
+        int b = t < a.T ? a.tok_seq[t] : -1, pos = 0, p0 = 0, end = 0, slot = 0, page = -1;
+        if (b >= 0) {
+            pos = a.tok_pos[t];
+            p0 = a.seq_pos0[b];
+            end = p0 + a.seq_start[b + 1] - a.seq_start[b];
+            slot = a.seq_slot[b];
+            const bool keep = a.pool && !a.no_store && (a.ring <= 0 || pos >= end - a.ring);
+            const int entry = a.ring > 0 ? pos % a.ring : pos;
+            if (keep) page = a.ptab[(long long)slot * a.ptab_stride + entry / PAGE_TOKENS];
+        }
+        r_seq[i] = b; r_pos[i] = pos; r_p0[i] = p0; r_end[i] = end; r_slot[i] = slot; r_page[i] = page;
+    }
+    __syncthreads();
+    if (c >= C) return;
     const int cr = c < a.QC ? c : c - a.QC;
     const int e = cr % max(a.sub, 1);
     const bool turned = c < a.QC + a.KC && a.rate && e < a.rot;
+    const float rate = turned ? a.rate[e >> 1] : 0.f;
     const float b0 = a.bias ? a.bias[c] : 0.f, b1 = a.bias ? a.bias[c + 1] : 0.f;
     float w0[K], w1[K];
 #pragma unroll
@@ -201,13 +222,15 @@ tap_rotate_pairs_kernel(const TapRotArgs a) {
             u[r].y += b1;
         }
     }
+    // where a key pair lies inside its entry: the same for every row
+    const bool is_key = c >= a.QC && cr < a.KC;
+    const int g = c < a.QC ? 0 : (is_key ? cr / a.KW : (cr - a.KC) / max(a.DV, 1));
+    const int off = c < a.QC ? 0 : (is_key ? cr - g * a.KW : cr - a.KC - g * a.DV);
 #pragma unroll
     for (int i = 0; i < TP_TOK; ++i) {
         const int t = t0 + i;
-        if (t >= a.T) break;
-        const int b = a.tok_seq[t];
-        if (b < 0) continue;
-        const int pos = a.tok_pos[t], p0 = a.seq_pos0[b];
+        if (r_seq[i] < 0) continue;
+        const int pos = r_pos[i], p0 = r_p0[i];
         float y0 = 0.f, y1 = 0.f;
 #pragma unroll
         for (int j = 0; j < K; ++j) {
@@ -216,7 +239,7 @@ tap_rotate_pairs_kernel(const TapRotArgs a) {
             if (s < p0) {
                 x0 = x1 = 0.f;
                 if (s >= 0) {
-                    const float* st = a.state + (long long)a.seq_slot[b] * a.state_stride + (long long)(s % K) * C + c;
+                    const float* st = a.state + (long long)r_slot[i] * a.state_stride + (long long)(s % K) * C + c;
                     x0 = st[0];
                     x1 = st[1];
                 }
@@ -224,10 +247,16 @@ tap_rotate_pairs_kernel(const TapRotArgs a) {
             y0 = fmaf(w0[j], x0, y0);
             y1 = fmaf(w1[j], x1, y1);
         }
+        if (a.from_zero && K > 1 && pos >= r_end[i] - (K - 1)) {
+            // the filter's state after the step: the projected rows of the sequence's last K - 1 positions
+            float* st = a.state + (long long)r_slot[i] * a.state_stride + (long long)(pos % K) * C + c;
+            st[0] = u[i + K - 1].x;
+            st[1] = u[i + K - 1].y;
+        }
         float v0 = y0, v1 = y1;
         if (turned) {
             float sn, cs;
-            sincosf((float)pos * a.rate[e >> 1], &sn, &cs);
+            sincosf((float)pos * rate, &sn, &cs);
             sn *= a.mag;
             cs *= a.mag;
             v0 = y0 * cs - y1 * sn;
@@ -240,25 +269,17 @@ tap_rotate_pairs_kernel(const TapRotArgs a) {
         if (a.rows_out) {
             T* o = (T*)a.q_out + (long long)t * a.ldq + a.QC;
             store_pair(o + cr, v0, v1);
-            if (cr < a.KC && a.value_from_key) store_pair(o + a.KC + cr, y0, y1);
+            if (is_key && a.value_from_key) store_pair(o + a.KC + cr, y0, y1);
         }
-        bool keep = !a.no_store;
-        int entry = pos;
-        if (a.ring > 0) {
-            const int end = p0 + a.seq_start[b + 1] - a.seq_start[b];
-            keep = keep && pos >= end - a.ring;
-            entry = pos % a.ring;
-        }
-        if (!keep) continue;
-        const int page = a.ptab[(long long)a.seq_slot[b] * a.ptab_stride + entry / PAGE_TOKENS], row = entry % PAGE_TOKENS;
-        if (cr < a.KC) {
-            const int g = cr / a.KW, off = cr - g * a.KW;
-            store_pair(kv_tile((T*)a.pool, 0, a.pages, page, g, a.G, a.HDC) + (long long)row * a.HDC + off, v0, v1);
-            if (a.value_from_key)
-                store_pair(kv_tile((T*)a.pool, 1, a.pages, page, g, a.G, a.HDC) + (long long)row * a.HDC + off, y0, y1);
+        const int page = r_page[i];
+        if (page < 0) continue;
+        const int entry = a.ring > 0 ? pos % a.ring : pos;
+        const long long at = (long long)(entry % PAGE_TOKENS) * a.HDC + off;
+        if (is_key) {
+            store_pair(kv_tile((T*)a.pool, 0, a.pages, page, g, a.G, a.HDC) + at, v0, v1);
+            if (a.value_from_key) store_pair(kv_tile((T*)a.pool, 1, a.pages, page, g, a.G, a.HDC) + at, y0, y1);
         } else {
-            const int cv = cr - a.KC, g = cv / a.DV, off = cv - g * a.DV;
-            store_pair(kv_tile((T*)a.pool, 1, a.pages, page, g, a.G, a.HDC) + (long long)row * a.HDC + off, v0, v1);
+            store_pair(kv_tile((T*)a.pool, 1, a.pages, page, g, a.G, a.HDC) + at, v0, v1);
         }
     }
 }
@@ -322,18 +343,20 @@ extern "C" int cm_tap_rotate_store(int dt, const TapRotArgs* args, cudaStream_t 
     if (a.ring < 0 || a.ring % PAGE_TOKENS) CM_REFUSE("tap_rotate_store: a ring of %d entries (whole pages)", a.ring);
     const bool many = a.T >= 512 && !a.one_token_each;               // long steps: four tokens a thread
     dim3 grid(many ? (a.T + 3) / 4 : a.T, (C + TR_THREADS - 1) / TR_THREADS), sgrid((C + TR_THREADS - 1) / TR_THREADS, a.B);
+    const bool inline_state = a.from_zero && (dt == DT_F32 ? tap_pairs_fit<float>(a) : tap_pairs_fit<bf16>(a));
+    if (!inline_state) a.from_zero = 0;
     if (dt == DT_F32) {
         if (tap_pairs_fit<float>(a)) launch_tap_pairs<float>(a, st);
         else if (many) cm_launch(tap_rotate_store_kernel<float, 4>, grid, TR_THREADS, 0, st, a);
         else cm_launch(tap_rotate_store_kernel<float, 1>, grid, TR_THREADS, 0, st, a);
         CM_CHECK_LAUNCH();
-        if (!a.one_token_each && a.K > 1) cm_launch(tap_state_kernel<float>, sgrid, TR_THREADS, 0, st, a);
+        if (!a.one_token_each && a.K > 1 && !inline_state) cm_launch(tap_state_kernel<float>, sgrid, TR_THREADS, 0, st, a);
     } else if (dt == DT_BF16) {
         if (tap_pairs_fit<bf16>(a)) launch_tap_pairs<bf16>(a, st);
         else if (many) cm_launch(tap_rotate_store_kernel<bf16, 4>, grid, TR_THREADS, 0, st, a);
         else cm_launch(tap_rotate_store_kernel<bf16, 1>, grid, TR_THREADS, 0, st, a);
         CM_CHECK_LAUNCH();
-        if (!a.one_token_each && a.K > 1) cm_launch(tap_state_kernel<bf16>, sgrid, TR_THREADS, 0, st, a);
+        if (!a.one_token_each && a.K > 1 && !inline_state) cm_launch(tap_state_kernel<bf16>, sgrid, TR_THREADS, 0, st, a);
     } else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();

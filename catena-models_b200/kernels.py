@@ -977,11 +977,11 @@ class _TapRotArgs(ctypes.Structure):
                 ("rate", _vp), ("mag", _f), ("tok_seq", _vp), ("tok_pos", _vp), ("seq_start", _vp), ("seq_pos0", _vp),
                 ("seq_slot", _vp)] + [(n, _i) for n in ("T", "B", "QC", "KC", "VC", "K", "sub", "rot", "G", "KW", "DV", "HDC",
                                                         "one_token_each", "interleaved", "value_from_key", "ring",
-                                                        "no_store", "rows_out")]
+                                                        "no_store", "rows_out", "from_zero")]
 
 
 def tap_rotate_store(proj, bias, taps, state, q_out, batch, q_channels, sub, rate, mag, kv=None, one_token_each=False,
-                     interleaved=False, value_from_key=False, ring=0, store=True, rows_out=False):
+                     interleaved=False, value_from_key=False, ring=0, store=True, rows_out=False, from_zero=False):
     """Short causal taps over the leading channels of the projected rows `proj` (q, then k and v when this layer
     has them), the partial rotation of q and k, and the cache write.  bias float32 [C] or None; taps float32
     [C, K]; state float32 [slots, >= K C] (a ring of the last K projected rows of every sequence, moved on by
@@ -990,7 +990,9 @@ def tap_rotate_store(proj, bias, taps, state, q_out, batch, q_channels, sub, rat
     width): this layer's pages [2, pages, G, PAGE_TOKENS, HDC]; keys and values follow q in `proj`.
     `interleaved`: the rotation pairs channel 2i with 2i + 1.  `value_from_key`: there are no value channels (value
     row width 0 in `kv`); a position's value is its key before the rotation.  `ring`: the pages are a ring of that many
-    entries.  `store` False leaves the cache alone.  `rows_out`: q_out rows are [q | turned k | v]."""
+    entries.  `store` False leaves the cache alone.  `rows_out`: q_out rows are [q | turned k | v].  `from_zero`: every
+    sequence of the step starts at position 0 (a whole-prompt step), so nothing reads the state and the form for long
+    interleaved steps writes it in its one launch."""
     T = proj.shape[0]
     C, K = taps.shape
     G = KW = DV = HDC = 0
@@ -1014,9 +1016,9 @@ def tap_rotate_store(proj, bias, taps, state, q_out, batch, q_channels, sub, rat
                     seq_pos0=_ptr(batch.seq_pos0), seq_slot=_ptr(batch.seq_slot), T=T, B=batch.B, QC=q_channels,
                     KC=G * KW, VC=G * DV, K=K, sub=sub, rot=0 if rate is None else 2 * rate.numel(), G=G, KW=KW, DV=DV,
                     HDC=HDC, one_token_each=int(one_token_each), interleaved=int(interleaved),
-                    value_from_key=int(value_from_key), ring=int(ring), no_store=int(not store), rows_out=int(rows_out))
+                    value_from_key=int(value_from_key), ring=int(ring), no_store=int(not store), rows_out=int(rows_out), from_zero=int(from_zero))
     _check(lib().cm_tap_rotate_store(dtype_code(proj.dtype), ctypes.byref(a), _stream()), "tap_rotate_store",
-           1 if one_token_each or K < 2 else 2,
+           1 if one_token_each or K < 2 or (from_zero and interleaved and T >= 64 and K <= 4) else 2,
            cost=lambda: (f"{T}x{C}, {K} taps", 2 * T * C * proj.element_size(), 2 * K * T * C))
 
 

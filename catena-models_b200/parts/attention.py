@@ -172,7 +172,7 @@ class GQAttention(Mixer):
                                  getattr(self.position, "magnitude", 1.0),
                                  kv=(kv.pool, kv.pages, kv.ptab, KVH, HD, 0), one_token_each=decode,
                                  interleaved=self.position.pairing == "interleaved", value_from_key=True, ring=kv.ring,
-                                 store=not batch.append, rows_out=not decode)
+                                 store=not batch.append, rows_out=not decode, from_zero=batch.prefill)
         q = packed[:, :QS]
         ctx = torch.empty((batch.T, QS), dtype=x.dtype, device=x.device)
         if decode:

@@ -378,3 +378,35 @@ def test_greedy_generation_through_the_library(folders, plains, dtype):
             if tok != best:
                 gap = float(row[best] - row[tok]) / float(row.abs().max())
                 assert dtype == "bfloat16" and gap < 0.03, (tok, best, gap)
+
+
+def test_command_line(folders, plains, tmp_path):
+    """The library's command line on a model folder (greedy tokens against the plain statement) and on random weights
+    from a configuration file (its prompt and decode timings)."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg, tensors = plains["C"]
+    p1, p2 = tiny.prompt(6, cfg["vocab"], 1), tiny.prompt(13, cfg["vocab"], 2)
+    cmd = [sys.executable, "-m", "catena_models_b200", "--model", folders["C"], "--dtype", "float32", "-n", "5",
+           "--ignore-eos", "--prompt", " ".join(map(str, p1)), "--prompt", ",".join(map(str, p2))]
+    run = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stderr
+    lines = [list(map(int, l.split())) for l in run.stdout.strip().splitlines()]
+    want = []
+    for p in (p1, p2):
+        seq = list(p)
+        for _ in range(5):
+            seq.append(int(plain.forward(seq, tensors, cfg)[0][-1].argmax()))
+        want.append(seq[len(p):])
+    assert [l[-5:] for l in lines] == want
+    conf = tmp_path / "c.json"
+    conf.write_text(json.dumps(tiny.TINY_M))
+    bench = subprocess.run([sys.executable, "-m", "catena_models_b200", "--random", str(conf), "--bench", "--pp", "200",
+                            "--tg", "6", "--tg-context", "150", "--batch", "2"], cwd=root, capture_output=True,
+                           text=True, timeout=600)
+    assert bench.returncode == 0, bench.stderr
+    assert "pp200x2" in bench.stdout and "tg6/ctx150x2" in bench.stdout

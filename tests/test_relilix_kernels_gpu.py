@@ -271,7 +271,8 @@ def test_taps_with_interleaved_rotation_and_values_from_the_keys(K, dtype, tol, 
         single = all(lens[i] == 1 and at[i] > 0 for i in live)
         out = torch.full((b.T, QC + 2 * KC), float("nan"), dtype=dtype, device=DEV)
         K.tap_rotate_store(rows, None, w.to(DEV), state, out, b, QC, HD, rate, mag, kv=(pool, 4 * pages_per, ptab, G, HD, 0),
-                           one_token_each=single, interleaved=True, value_from_key=True, ring=ring, rows_out=True)
+                           one_token_each=single, interleaved=True, value_from_key=True, ring=ring, rows_out=True,
+                           from_zero=all(at[i] == 0 for i in live))
         ref = torch.cat([want[i][at[i]:at[i] + lens[i]] for i in live])
         assert float((out.double().cpu() - ref).abs().max()) < tol * max(1.0, float(ref.abs().max()))
         for i in live:
