@@ -582,17 +582,17 @@ def maferax_config(size, vocab=VOCAB):
 def relilix_config(size, vocab=VOCAB):
     """For `--compare relilix`: eight layers of the Relilix decoder at the same width, heads and feed-forward widths as the
     Maferax model above: four attention layers behind four taps (the attention's heads of 64 channels over the key/value
-    heads, a window of 1,024 tokens, scores capped at 50, the values taken from the keys) and four latent attention layers
+    heads, a window of 1,024 tokens, scores capped at 30, the values taken from the keys) and four latent attention layers
     of Maferax's sizes with rescaled rotation, the last of which reads the latents of the one before; dense and routed
     feed-forwards in turn, the routed ones with clamped experts in four groups of which two stay open and a shared expert."""
     z = COMPARE_SIZES[size]
     att = lambda mlp: dict(type="attention", mlp=mlp, mixer=dict(
-        heads=z["heads"], kv_heads=z["kv_heads"], dim=z["head"], vdim=z["head"], conv=4, scale=z["head"] ** -0.5, softcap=50.0,
+        heads=z["heads"], kv_heads=z["kv_heads"], dim=z["head"], vdim=z["head"], conv=4, scale=z["head"] ** -0.5, softcap=30.0,
         mask=dict(size=1024), rot=dict(dims=z["head"] // 2, base=1000000.0)))
     lat = lambda mlp, kv_from=None: dict(type="latent_attention", mlp=mlp, mixer=dict(
         heads=z["heads"], dim=z["head"], rot_dim=32, vdim=z["head"], kv_rank=z["width"] // 4, q_rank=3 * z["width"] // 8,
         scale=(z["head"] + 32) ** -0.5,
-        rot=dict(dims=32, base=1000000.0, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0)),
+        rot=dict(dims=32, base=1000000.0, scaling=dict(factor=4.0, original=4096, fast=16.0, slow=2.0)),
         **({} if kv_from is None else dict(kv_from=kv_from))))
     dense = dict(kind="dense", ff=z["ff"])
     moe = dict(kind="moe", expert=dict(ff=z["expert_ff"], limit=7.0), shared=dict(ff=z["expert_ff"], limit=7.0),

@@ -56,13 +56,13 @@ def _views(q, k, v, QH, KVH, HD):
 
 
 # ------------------------------------------------------------------------------------------ whole prompts
-@pytest.mark.parametrize("cap", [2.0, 50.0])
+@pytest.mark.parametrize("cap", [2.0, 40.0])
 @pytest.mark.parametrize("impl, dtype, QH, KVH, HD, T, window", [
     ("simt", torch.float32, 4, 2, 24, 150, 37), ("simt", torch.bfloat16, 3, 1, 40, 130, 0), ("simt", torch.float32, 2, 2, 16, 90, 3),
     ("mma", torch.bfloat16, 4, 2, 64, 300, 100), ("mma", torch.bfloat16, 2, 1, 112, 200, 0), ("mma", torch.bfloat16, 6, 6, 16, 140, 64),
     ("tc", torch.bfloat16, 4, 2, 64, 900, 0), ("tc", torch.bfloat16, 2, 1, 128, 1000, 800), ("tc", torch.bfloat16, 2, 2, 64, 700, 130)])
 def test_capped_scores_in_prompt_attention(K, impl, dtype, QH, KVH, HD, T, window, cap):
-    """Random rows whose raw scores reach several times a cap of 2, or a fifth of a cap of 50 (where the tcgen05 kernel forms
+    """Random rows whose raw scores reach several times a cap of 2, or a quarter of a cap of 40 (where the tcgen05 kernel forms
     the tanh of most rows by its series): the result follows the capped scores, not the raw ones."""
     if cap > 2.0 and impl != "tc":
         pytest.skip("one form of the tanh")
@@ -117,7 +117,7 @@ def test_a_far_key_under_the_cap_and_the_windows_edge_in_prompts(K, impl, dtype,
 
 # ------------------------------------------------------------------------------------------ single tokens
 @pytest.mark.parametrize("dtype, tensor_cores", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
-@pytest.mark.parametrize("QH, KVH, HD, window", [(4, 2, 16, 0), (6, 1, 128, 72), (5, 5, 32, 70), (8, 2, 64, 300), (2, 1, 48, 0)])
+@pytest.mark.parametrize("QH, KVH, HD, window", [(4, 2, 16, 0), (6, 3, 128, 90), (5, 5, 32, 70), (8, 2, 64, 300), (2, 1, 48, 0)])
 def test_capped_scores_in_single_token_attention(K, dtype, tensor_cores, QH, KVH, HD, window):
     K.set_decode_attention_tensor_cores(tensor_cores)
     try:
@@ -155,7 +155,7 @@ def test_a_far_key_under_the_cap_and_the_windows_edge_in_single_tokens(K, dtype,
     try:
         QH = KVH = 1
         HD, n, cap = 16, 500, 15.0
-        for window, far, seen in [(0, 3, True), (200, n - 200, True), (200, n - 201, False), (72, n - 72, True), (72, n - 73, False)]:
+        for window, far, seen in [(0, 3, True), (200, n - 200, True), (200, n - 201, False), (88, n - 88, True), (88, n - 89, False)]:
             ring = (window + 63) // 64 * 64 if window else 0
             kv = [torch.randn(n, 2, KVH, HD, generator=torch.Generator().manual_seed(1)) * 0.1]
             kv[0][far, 0, 0] = 0.0
@@ -180,7 +180,7 @@ def test_a_far_key_under_the_cap_and_the_windows_edge_in_single_tokens(K, dtype,
 
 # ------------------------------------------------------------------------------------------ portions on top of a cache
 @pytest.mark.parametrize("impl, dtype, QH, KVH, HD, window", [("simt", torch.float32, 4, 2, 24, 50), ("mma", torch.bfloat16, 4, 2, 64, 0),
-                                                              ("mma", torch.bfloat16, 2, 1, 128, 72), ("tc", torch.bfloat16, 4, 1, 64, 600),
+                                                              ("mma", torch.bfloat16, 2, 1, 128, 90), ("tc", torch.bfloat16, 4, 1, 64, 600),
                                                               ("tc", torch.bfloat16, 2, 2, 128, 0)])
 def test_capped_scores_in_portions_on_top_of_held_tokens(K, impl, dtype, QH, KVH, HD, window):
     past, new, cap, scale = [0, 700, 65], [40, 130, 200], 2.0, HD ** -0.5
