@@ -40,7 +40,7 @@ class AttentionConfig:
     kv_heads: int
     dim: int
     vdim: int
-    taps: int                # 1: no filter (and no filter tensors)
+    taps: int                # 0: no filter and no filter tensors; 1: one tap, a factor per channel
     scale: float
     softcap: float           # 0: none
     window: int              # 0: every earlier position is seen
@@ -141,7 +141,7 @@ class RelilixConfig:
             heads, dim = m.integer("heads", minimum=1), m.integer("dim", minimum=1)
             mask = section(r, m.data, "mask", where + "mixer.", required=False)
             mixer = AttentionConfig(heads, m.integer("kv_heads", default=heads, minimum=1), dim,
-                                    m.integer("vdim", default=dim, minimum=1), m.integer("conv", default=1, minimum=1),
+                                    m.integer("vdim", default=dim, minimum=1), m.integer("conv", default=0, minimum=0),
                                     m.number("scale", positive=True), m.number("softcap", default=0.0),
                                     mask.integer("size", default=0, minimum=0) if mask else 0, _rotation(r, m, where))
         elif m:

@@ -25,10 +25,10 @@ zero columns of the output projection); `out_dtype` = "float32" leaves the outpu
 
 `softcap` = c > 0 bounds every score before the mask and the softmax: s <- c * tanh(s / c), s = (q . k) * scale.
 
-`taps` = K > 1 puts a short causal filter behind the query and key projections, one set of K taps per channel
+`taps` = K >= 1 puts a short causal filter behind the query and key projections, one set of K taps per channel
 (`q_taps`, `k_taps` name the tensors, [channels, K]): y_t = sum_j w[:, j] u_(t - K + 1 + j), zeros before the sequence's
-start, before the rotation.  The last K projected rows of a sequence are then part of the layer's state (float32, a
-ring beside the key/value pages).  `value_from_key`: the layer has no value projection; a position's value is its key
+start, before the rotation (K = 1 is a factor per channel; 0: no filter and no tensors).  For K > 1 the last K projected
+rows of a sequence are part of the layer's state (float32, a ring beside the key/value pages).  `value_from_key`: the layer has no value projection; a position's value is its key
 as the filter leaves it, before the rotation.  Filter, rotation and the cache write are one kernel
 (`kernels.tap_rotate_store`), which leaves the step's rows as [q | turned k | v] for the attention kernels.
 """
@@ -52,7 +52,7 @@ class GQAttention(Mixer):
 
     def __init__(self, prefix, hidden, heads, kv_heads, head_dim, window, position, qk_norm_eps,
                  output_gate, names=None, shares_kv=False, scale=None, sink_name=None, q_temp=None, value_dim=None,
-                 out_dtype=None, softcap=0.0, taps=1, value_from_key=False):
+                 out_dtype=None, softcap=0.0, taps=0, value_from_key=False):
         names = names or {}
         n = lambda key, default: prefix + names.get(key, default)
         qk_dim, v_dim = head_dim, value_dim or head_dim
@@ -64,14 +64,14 @@ class GQAttention(Mixer):
         pad_k = (kv_heads, qk_dim, head_dim) if head_dim != qk_dim else None
         pad_v = (kv_heads, v_dim, head_dim) if head_dim != v_dim else None
         self.qk_dim, self.v_dim = qk_dim, v_dim
-        self.softcap, self.taps, self.value_from_key = float(softcap or 0.0), int(taps or 1), bool(value_from_key)
-        if self.softcap < 0.0 or self.taps < 1:
-            raise ValueError("GQAttention: softcap >= 0 and taps >= 1")
+        self.softcap, self.taps, self.value_from_key = float(softcap or 0.0), int(taps or 0), bool(value_from_key)
+        if self.softcap < 0.0 or self.taps < 0:
+            raise ValueError("GQAttention: softcap >= 0 and taps >= 0")
         if self.value_from_key and (v_dim != qk_dim or shares_kv):
             raise ValueError("GQAttention: values that are the keys have the keys' size, and a layer of its own keys")
-        if (self.taps > 1 or self.value_from_key) and (shares_kv or qk_norm_eps is not None or q_temp or output_gate):
+        if (self.taps > 0 or self.value_from_key) and (shares_kv or qk_norm_eps is not None or q_temp or output_gate):
             raise ValueError("GQAttention: the filtered form has neither head norm, query temperature, gate nor shared keys")
-        self.filtered = self.taps > 1 or self.value_from_key
+        self.filtered = self.taps > 0 or self.value_from_key
         if self.filtered:
             self.fused_decode_ok = False       # its decode step runs a kernel of its own between the products
         self.sink_name, self.sink = (prefix + sink_name if sink_name else None), None
@@ -104,7 +104,7 @@ class GQAttention(Mixer):
                           head_cols=(heads, v_dim, head_dim) if head_dim != v_dim else None)
         self.q_norm_name, self.k_norm_name = n("q_norm", "attn_q_norm.weight"), n("k_norm", "attn_k_norm.weight")
         self.q_norm_w = self.k_norm_w = None
-        self.tap_names = (n("q_taps", "attn_q.conv"), n("k_taps", "attn_k.conv")) if self.taps > 1 else ()
+        self.tap_names = (n("q_taps", "attn_q.conv"), n("k_taps", "attn_k.conv")) if self.taps > 0 else ()
         self.tap_w = None
         # 1/sqrt(head_dim) in float32, as the reference bakes it (src/catena/qwen35_wmma_attention.hex:3-22)
         self.scale = float(torch.tensor(1.0, dtype=torch.float32) / torch.sqrt(torch.tensor(float(qk_dim), dtype=torch.float32)))
@@ -116,7 +116,7 @@ class GQAttention(Mixer):
 
     def tensor_specs(self):
         specs = [TensorSpec(self.sink_name, (self.heads,), "vector")] if self.sink_name else []
-        if self.taps > 1:
+        if self.taps > 0:
             specs += [TensorSpec(self.tap_names[0], (self.heads * self.qk_dim, self.taps), "conv"),
                       TensorSpec(self.tap_names[1], (self.kv_heads * self.qk_dim, self.taps), "conv")]
         if self.qk_norm_eps is None:
@@ -129,7 +129,7 @@ class GQAttention(Mixer):
     def bind(self, tensors, rt):
         self._bound = []
         if self.filtered:
-            if self.taps > 1:
+            if self.taps > 0:
                 # heads padded with zero channels get taps of zero
                 padded = []
                 for t in self.tap_names:

@@ -87,7 +87,7 @@ def window_attention(h, P, p, m, rd=ident):
     H, G, D = m["heads"], m.get("kv_heads", m["heads"]), m["dim"]
     pos = torch.arange(T)
     q, k = rd(h @ P[p + "q"].T), rd(h @ P[p + "k"].T)
-    if m.get("conv", 1) > 1:
+    if m.get("conv"):
         q, k = taps(q, P[p + "q.conv"]), taps(k, P[p + "k.conv"])
     q, k = q.view(T, H, D), k.view(T, G, D)
     v = rd(k)

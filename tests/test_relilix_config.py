@@ -30,7 +30,9 @@ def test_fields_of_every_layer():
 def test_what_may_be_left_out():
     _, cfg = config_from_dict(tiny.TINY_C)
     a = cfg.layers[0].mixer
-    assert (a.taps, a.window, a.softcap, a.rot) == (1, 0, 0.0, None)
+    assert (a.taps, a.window, a.softcap, a.rot) == (0, 0, 0.0, None)
+    arch, d = config_from_dict(tiny.ONLY_DENSE)
+    assert d.layers[0].mixer.taps == 1 and {s.name: tuple(s.shape) for s in arch.define(d).tensor_specs()}["l0.mix.k.conv"] == (8, 1)
     assert cfg.layers[2].mlp is None
     _, b = config_from_dict(tiny.TINY_B)
     assert b.layers[0].mlp.shared is None and b.layers[0].mlp.groups == 0

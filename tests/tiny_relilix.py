@@ -103,7 +103,8 @@ TINY_L = model(120, 64, 1e-6, 1.5, [
 ONLY_ATTENTION = model(64, 32, 1e-6, 1.0, [attention(4, 2, 16, 4, 24, 0.3, 3.0, rot(16, 200.0), None)])
 ONLY_LATENT = model(64, 32, 1e-6, 1.0, [latent(4, 16, 8, 24, 24, 12, 0.25, rot(8, 200.0, (2.0, 48, 8.0, 1.0)), None)])
 ONLY_MOE = model(64, 24, 1e-6, 1.0, [attention(1, 1, 8, 0, 0, 0.3, 0.0, None, moe(16, 0.7, 8, 3, groups=(4, 2), shared=(24, 1.1)))])
-ONLY_DENSE = model(64, 24, 1e-6, 2.0, [attention(1, 1, 8, 0, 0, 0.3, 0.0, None, dense(56))])
+# ... and a filter of one tap: a factor per channel, no state
+ONLY_DENSE = model(64, 24, 1e-6, 2.0, [attention(1, 1, 8, 1, 0, 0.3, 0.0, None, dense(56))])
 
 ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "M": TINY_M, "L": TINY_L, "attention": ONLY_ATTENTION,
        "latent": ONLY_LATENT, "moe": ONLY_MOE, "dense": ONLY_DENSE}
