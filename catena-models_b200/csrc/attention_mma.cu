@@ -192,10 +192,23 @@ attn_prefill_mma_kernel(bf16* __restrict__ ctx, long long ldc, const bf16* __res
             }
         }
         if (cap_in > 0.f) {
+            // scores that all stay within a quarter of the cap take the tanh's series (no special-function operation)
+            float am = 0.f;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) s[j][i] = tanh_fast(s[j][i] * cap_in);
+                for (int i = 0; i < 4; ++i) am = fmaxf(am, fabsf(s[j][i]));
+            if (am * cap_in < TANH_SERIES_BOUND) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) s[j][i] = tanh_series(s[j][i] * cap_in);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) s[j][i] = tanh_fast(s[j][i] * cap_in);
+            }
         }
         // ---- mask, running maximum
         const bool edge = key0 + FA_BK - 1 > q0 + warp * 16 || key0 + FA_BK > len ||
@@ -489,10 +502,22 @@ attn_decode_mma_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, 
             if (next_live) request(Ks, 0, next_idx);
             cp_async_commit();
             if (cap_in > 0.f) {                 // bounded scores: tanh(s scale / cap), and cap log2 e in the exponent
+                float am = 0.f;
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) s[j][i] = tanh_fast(s[j][i] * cap_in);
+                    for (int i = 0; i < 4; ++i) am = fmaxf(am, fabsf(s[j][i]));
+                if (am * cap_in < TANH_SERIES_BOUND) {          // all within a quarter of the cap: the series
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) s[j][i] = tanh_series(s[j][i] * cap_in);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) s[j][i] = tanh_fast(s[j][i] * cap_in);
+                }
             }
             // visibility of the page's entries (columns of s); raw scores, the scale goes into the exponent
             if (mask_all || (page_idx + 1) * FD_PAGE > n_entries) {
