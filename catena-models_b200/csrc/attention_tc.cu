@@ -513,8 +513,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 tmem_load_wait();
                 if (past.cap_in > 0.f) {                             // bounded scores: tanh(s scale / cap); cap log2 e is in scale_log2
                     // a row whose scores all stay within a quarter of the cap takes the series, which needs no special-function
-                    // operation (the softmax keeps that unit busy); any other row (also one with a score that is not a number,
-                    // from rows that are not the sequence's and are masked below) the exponential form
+                    // operation (the softmax keeps that unit busy); any other row the exponential form.  Scores of rows that
+                    // are not the sequence's may be anything, also no number: whatever either form makes of them, the mask
+                    // below replaces it
                     float am4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                     for (int c = 0; c < FT_TILE; ++c) am4[c & 3] = fmaxf(am4[c & 3], fabsf(v[c]));
